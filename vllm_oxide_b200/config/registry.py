@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and model builder.
 
 The reference serves one model and has no registry; this engine keys everything on
-`architectures[0]` of config.json. An entry names the typed configuration class that
+`architectures[0]` (or the string `architecture`) of config.json. An entry names the typed configuration class that
 reads config.json, the manifest of tensor names and shapes the architecture expects, and a
 builder that turns (configuration, weights) into a `ModelSpec` of parts. Unknown names fail with the list of known ones.
 """
@@ -40,8 +40,10 @@ def known_architectures():
 
 def architecture_for(config_dict: dict, where: str = "config.json") -> Architecture:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]           # the name given as one string
     if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
-        raise ConfigError(f"{where}: 'architectures' must be a list with the model class name")
+        raise ConfigError(f"{where}: 'architectures' must be a list with the model class name (or 'architecture' the name)")
     try:
         return _REGISTRY[archs[0]]
     except KeyError:

@@ -1,0 +1,306 @@
+// Linear recurrences over a matrix state per request and head: the state S [K key channels,
+// V value channels] is float32, lives in the request's state slot and is carried from token to
+// token, across steps:
+//     mode 0 (delta rule with decay):  S_t = diag(w_t) S_(t-1) - b_t (u_t^T S_(t-1)) + k_t v_t^T
+//     mode 1 (fixed decay per head):   S_t = d_h S_(t-1) + k_t v_t^T
+//     o_t = S_t^T r_t
+// w_t, b_t, u_t are float32 vectors per token, head and key channel, prepared by vob_delta_prep (or
+// by anything else that writes them); d_h is one number per head.
+//
+// Every value column of S evolves on its own, so the work is cut by columns: a block owns VT
+// columns of one head of one request, KS threads share a column (thread q of them holds key
+// channels q, q + KS, ... in registers) and the two dot products over key channels are finished
+// by shuffles among those KS lanes, in a fixed order. The block walks the request's rows of this
+// step in order, CT tokens at a time staged in shared memory. A step of one token is the same
+// kernel: read the state, one update, write it back (bound by the state's bytes). The arithmetic
+// of a token never depends on how the tokens were cut into steps or what else is in the batch.
+//
+// Beside the scan: vob_delta_prep (unit key, removal rate, decay from its low-rank projection),
+// vob_rotate_scale (rotary positions on the first `rot` features of every head, times a scale,
+// to float32) and vob_recurrence_post (per-head RMS norm of o, an optional weight, a gate).
+#include "common.cuh"
+VOB_PDL_SWITCH(recurrence)
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ---------------------------------------------------------------------------------------------
+// Delta-rule preparation, per token t, head h and key channel c (ch = h * K + c):
+//   u = k / sqrt(sum_c k^2 + 1e-6)                      (the key at unit length, per head)
+//   a = sigmoid(a_in + a_bias)                          (removal rate)       b = a * u
+//   w = exp(-exp(-1/2) * sigmoid(w0 + sum_j w2[ch, j] * tanh(low[j])))       (decay, in (0.545, 1))
+// k, a_in and low (the rank-R projection) are columns of one projection output `proj` [T, ld].
+// Launch: one block of 128 threads per (token, head). All arithmetic float32.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(const T* __restrict__ proj, long ld, int k_off, int a_off, int low_off, int R, const TW* __restrict__ w2,
+                  const float* __restrict__ w0, const float* __restrict__ a_bias, int H, int K, float* __restrict__ w_out,
+                  float* __restrict__ b_out, float* __restrict__ u_out) {
+    pdl_launch_dependents();
+    pdl_wait(41);
+    extern __shared__ float th[];          // tanh of the low-rank projection, R floats
+    __shared__ float red[4];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const T* row = proj + (size_t)t * ld;
+    for (int j = tid; j < R; j += blockDim.x) th[j] = tanhf(ld_f(row + low_off + j));
+    float ss = 0.f;
+    for (int c = tid; c < K; c += blockDim.x) {
+        const float kv = ld_f(row + k_off + h * K + c);
+        ss = fmaf(kv, kv, ss);
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf((red[0] + red[1]) + (red[2] + red[3]) + 1e-6f);
+    for (int c = tid; c < K; c += blockDim.x) {
+        const int ch = h * K + c;
+        const float kv = ld_f(row + k_off + ch);
+        const float u = kv * inv;
+        const float a = sigmoidf_(ld_f(row + a_off + ch) + a_bias[ch]);
+        float low = w0[ch];
+        const TW* wr = w2 + (size_t)ch * R;
+        for (int j = 0; j < R; ++j) low = fmaf(ld_f(wr + j), th[j], low);
+        const size_t o = (size_t)t * H * K + ch;
+        w_out[o] = expf(-0.6065306597126334f * sigmoidf_(low));
+        b_out[o] = a * u;
+        u_out[o] = u;
+    }
+}
+
+VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, int a_off, int low_off, int R, const void* w2,
+                              int w2_code, const float* w0, const float* a_bias, int T, int H, int K, float* w_out, float* b_out,
+                              float* u_out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || K <= 0 || R <= 0 || H > 65535 || (size_t)R * 4 > 40 * 1024) return VOB_ERR_BAD_ARG;
+    if (code != w2_code) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(delta_prep_kernel<ElemT, ElemT>, dim3(T, H), dim3(128), (size_t)R * 4, stream,
+                                              (const ElemT*)proj, ld, k_off, a_off, low_off, R, (const ElemT*)w2, w0, a_bias, H, K,
+                                              w_out, b_out, u_out));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rotary positions and a scale, to float32: for every head of D features, feature i < rot / 2 is
+// paired with feature i + rot / 2 and the pair (a, b) becomes (a cos - b sin, b cos + a sin) with
+// the angle float(position) * inv_freq[i]; features from `rot` on pass unchanged; everything is
+// multiplied by `scale`. src is a column range of a projection output [T, ld]; out [T, H * D].
+// Rows with a negative position (padding) are written as zeros.
+// Launch: one block of 128 threads per token.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+rotate_scale_kernel(const T* __restrict__ src, long ld, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                    int H, int D, int rot, float scale, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait(42);
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const T* row = src + (size_t)t * ld;
+    float* o = out + (size_t)t * H * D;
+    const int half = rot >> 1;
+    for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+        const int f = e % D;
+        float v = 0.f;
+        if (pos >= 0) {
+            if (f < rot) {
+                const int i = f < half ? f : f - half;
+                const float ang = (float)pos * inv_freq[i];
+                const float cs = cosf(ang), sn = sinf(ang);
+                const float a = ld_f(row + e - f + i), b = ld_f(row + e - f + i + half);
+                v = f < half ? a * cs - b * sn : b * cs + a * sn;
+            } else {
+                v = ld_f(row + e);
+            }
+            v *= scale;
+        }
+        o[e] = v;
+    }
+}
+
+VOB_EXPORT int vob_rotate_scale(const void* src, int code, long ld, const int* positions, const float* inv_freq, int T, int H,
+                                int D, int rot, float scale, float* out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || D <= 0 || rot < 0 || rot > D || (rot & 1)) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(rotate_scale_kernel<ElemT>, dim3(T), dim3(128), 0, stream, (const ElemT*)src, ld,
+                                              positions, inv_freq, H, D, rot, scale, out));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The scan. Grid (ceil(V / VT), H, requests); block VT * KS threads, lane = column * KS + q.
+// r, k: [T, >= H * K] with row strides; v: [T, >= H * V]; w, b, u: float32 [T, H * K] (mode 0) or
+// w = float32 [H] (mode 1); state float32 [slots, H, K, V]; o float32 [T, H * V].
+// A request's rows are seq_starts[s] .. seq_starts[s + 1] - 1 (none: the block leaves at once and
+// its state slot is not touched).
+// ---------------------------------------------------------------------------------------------
+template <int MODE, int KPT, typename TRK, typename TV>
+__global__ void __launch_bounds__(128)
+recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restrict__ k, long ld_k, const TV* __restrict__ v,
+                       long ld_v, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ u,
+                       float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
+                       float* __restrict__ o, int H, int K, int V, int KS, int VT, int CT) {
+    pdl_launch_dependents();
+    pdl_wait(43);
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int r0 = seq_starts[s], r1 = seq_starts[s + 1];
+    if (r1 <= r0) return;
+    extern __shared__ float sm[];
+    const int KPAD = KS * KPT;
+    float* sr = sm;                          // [CT][KPAD]
+    float* sk = sr + CT * KPAD;
+    float* sv = sk + CT * KPAD;              // [CT][VT]
+    float* sw = sv + CT * VT;                // mode 0 only: [CT][KPAD] each
+    float* sb = sw + CT * KPAD;
+    float* su = sb + CT * KPAD;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int q = tid % KS, jj = tid / KS;
+    const int j = blockIdx.x * VT + jj;
+    const bool col = j < V;
+    float* S_glob = state + ((size_t)state_slots[s] * H + h) * K * V;
+    float S[KPT];
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int c = q + i * KS;
+        S[i] = (col && c < K) ? S_glob[(size_t)c * V + j] : 0.f;
+    }
+    const float decay = MODE == 1 ? w[h] : 0.f;
+    for (int c0 = r0; c0 < r1; c0 += CT) {
+        const int n = min(CT, r1 - c0);
+        __syncthreads();                     // the tokens staged before have been used
+        for (int e = tid; e < n * KPAD; e += nthr) {
+            const int tt = e / KPAD, c = e - tt * KPAD;
+            const size_t row = (size_t)(c0 + tt);
+            const bool in = c < K;
+            sr[e] = in ? ld_f(r + row * ld_r + h * K + c) : 0.f;
+            sk[e] = in ? ld_f(k + row * ld_k + h * K + c) : 0.f;
+            if (MODE == 0) {
+                const size_t g = row * H * K + h * K + c;
+                sw[e] = in ? w[g] : 0.f;
+                sb[e] = in ? b[g] : 0.f;
+                su[e] = in ? u[g] : 0.f;
+            }
+        }
+        for (int e = tid; e < n * VT; e += nthr) {
+            const int tt = e / VT, c = e - tt * VT;
+            const int jv = blockIdx.x * VT + c;
+            sv[e] = jv < V ? ld_f(v + (size_t)(c0 + tt) * ld_v + h * V + jv) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float* pr = sr + tt * KPAD + q;
+            const float* pk = sk + tt * KPAD + q;
+            const float vj = sv[tt * VT + jj];
+            if (MODE == 0) {
+                const float* pw = sw + tt * KPAD + q;
+                const float* pb = sb + tt * KPAD + q;
+                const float* pu = su + tt * KPAD + q;
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) dot = fmaf(pu[i * KS], S[i], dot);
+                for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(pk[i * KS], vj, fmaf(pw[i * KS], S[i], -(pb[i * KS] * dot)));
+            } else {
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(pk[i * KS], vj, decay * S[i]);
+            }
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) acc = fmaf(pr[i * KS], S[i], acc);
+            for (int off = 1; off < KS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (q == 0 && col) o[(size_t)(c0 + tt) * H * V + h * V + j] = acc;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int c = q + i * KS;
+        if (col && c < K) S_glob[(size_t)c * V + j] = S[i];
+    }
+}
+
+// How the key channels are shared out: KS lanes per column (a power of two), KPT registers per lane.
+static inline void scan_split(int K, int* KS, int* KPT) {
+    int ks = K <= 128 ? 4 : K <= 256 ? 8 : K <= 512 ? 16 : 32;
+    int per = (K + ks - 1) / ks;
+    *KS = ks;
+    *KPT = per <= 8 ? 8 : per <= 16 ? 16 : 32;
+}
+
+template <int MODE, typename TRK, typename TV>
+static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const void* v, long ld_v, const float* w, const float* b,
+                       const float* u, float* state, const int* seq_starts, const int* state_slots, float* o, int seqs, int H, int K,
+                       int V, cudaStream_t stream) {
+    int KS, KPT;
+    scan_split(K, &KS, &KPT);
+    const int VT = 128 / KS;
+    const int KPAD = KS * KPT;
+    const size_t per_token = (size_t)((MODE == 0 ? 5 : 2) * KPAD + VT) * 4;
+    int CT = (int)(40 * 1024 / per_token);
+    CT = CT > 16 ? 16 : CT < 1 ? 1 : CT;
+    const size_t smem = per_token * CT;
+    dim3 grid((V + VT - 1) / VT, H, seqs), block(VT * KS);
+#define VOB_SCAN(P)                                                                                                            \
+    return vob_launch(recurrence_scan_kernel<MODE, P, TRK, TV>, grid, block, smem, stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, \
+                      (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, H, K, V, KS, VT, CT)
+    if (KPT == 8) VOB_SCAN(8);
+    if (KPT == 16) VOB_SCAN(16);
+    VOB_SCAN(32);
+#undef VOB_SCAN
+}
+
+VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const void* k, long ld_k, int rk_code, const void* v, long ld_v,
+                                   int v_code, const float* w, const float* b, const float* u, float* state, const int* seq_starts,
+                                   const int* state_slots, float* o, int seqs, int H, int K, int V, cudaStream_t stream) {
+    if (seqs <= 0) return 0;
+    if (H <= 0 || K <= 0 || V <= 0 || H > 65535 || seqs > 65535) return VOB_ERR_BAD_ARG;
+    if (K > 1024) return VOB_ERR_UNSUPPORTED;
+    if (mode == 0 && (!w || !b || !u)) return VOB_ERR_BAD_ARG;
+    if (mode == 1 && !w) return VOB_ERR_BAD_ARG;
+#define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, stream
+    if (mode == 0 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<0, float, float>(VOB_ARGS);
+    if (mode == 0 && rk_code == VOB_BF16 && v_code == VOB_BF16) return scan_launch<0, __nv_bfloat16, __nv_bfloat16>(VOB_ARGS);
+    if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<1, float, float>(VOB_ARGS);
+    if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_BF16) return scan_launch<1, float, __nv_bfloat16>(VOB_ARGS);
+#undef VOB_ARGS
+    return VOB_ERR_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------
+// After the scan, per token and head: out = o / sqrt(mean(o^2) + eps) * weight * gate(g), with
+// weight optional ([H * V] float32) and gate = sigmoid (0) or silu (1) of the gate projection g, a
+// column range of a projection output [T, ld_g]. out [T, H * V] in the activations' type.
+// Launch: one block of 128 threads per (token, head).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+recurrence_post_kernel(const float* __restrict__ o, const T* __restrict__ g, long ld_g, const float* __restrict__ weight,
+                       int gate_mode, float eps, int H, int V, T* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait(44);
+    __shared__ float red[4];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const float* orow = o + (size_t)t * H * V + h * V;
+    float ss = 0.f;
+    for (int c = tid; c < V; c += blockDim.x) ss = fmaf(orow[c], orow[c], ss);
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)V + eps);
+    for (int c = tid; c < V; c += blockDim.x) {
+        const float gv = ld_f(g + (size_t)t * ld_g + h * V + c);
+        const float sg = sigmoidf_(gv);
+        float val = orow[c] * inv;
+        if (weight) val *= weight[h * V + c];
+        val *= gate_mode == 1 ? gv * sg : sg;
+        st_f(out + (size_t)t * H * V + h * V + c, val);
+    }
+}
+
+VOB_EXPORT int vob_recurrence_post(const float* o, const void* g, int code, long ld_g, const float* weight, int gate_mode, float eps,
+                                   int T, int H, int V, void* out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || V <= 0 || H > 65535 || (gate_mode != 0 && gate_mode != 1)) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(recurrence_post_kernel<ElemT>, dim3(T, H), dim3(128), 0, stream, o, (const ElemT*)g, ld_g,
+                                              weight, gate_mode, eps, H, V, (ElemT*)out));
+    return 0;
+}

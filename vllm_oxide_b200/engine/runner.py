@@ -172,6 +172,7 @@ class ModelRunner:
         self.step_graph_after = int(getattr(engine, "step_graphs", 0))
         self.step_graph_replays = 0
         self._folded = None
+        self.after_block = None                 # debugging: a function (call number, residual, pending) run behind every block
         self._graph_launches = {}
         self._graph_pool = None
 
@@ -192,12 +193,14 @@ class ModelRunner:
         the head's chunk (logits and the normed rows)."""
         es = 2 if self.dtype == torch.bfloat16 else 4
         h, V = self.spec.hidden_size, self.spec.vocab_size
-        resid = aligned(rows * h * 4)
+        resid = aligned(rows * h * 4 * self.spec.residual_streams)
         pending = 2 * aligned(rows * h * es)
         block = max((b.workspace_bytes(rows, h, es) for b in self.spec.blocks), default=0)
         n = min(self.logit_chunk, rows)
         head = aligned(n * V * 4) + self.spec.final_norm.workspace_bytes(n, es)
-        total = resid + pending + max(block, head)
+        # an embedding may use scratch of its own beside the residual (gone before the first block runs)
+        embed = getattr(self.spec.embedding, "scratch_bytes", lambda r: 0)(rows)
+        total = resid + max(embed, pending + max(block, head))
         if self._can_fold(1):
             # steps of few rows run in folded form (FoldedState): residual, the next norm's input, the
             # partial sums of squares, and the blocks' folded scratch or the head
@@ -329,6 +332,8 @@ class ModelRunner:
             cache = self.pools.layer_cache(call.cache, call.write)
             state = self.pools.state.get(i)
             pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1])
+            if self.after_block is not None:
+                self.after_block(i, resid, pending)
         return resid, pending
 
     def _head(self, resid, pending, ctx: StepContext, num_logit_rows: int, logits_out: Optional[torch.Tensor],

@@ -90,7 +90,8 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 
 _fn_cache = {}
-_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling")
+_MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling",
+            "streams", "recurrence", "latent_attention")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -687,6 +688,217 @@ def _library_gemm_bf16(a, w, out):
         torch.mm(a, w.t(), out=out)
     else:
         torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
+
+
+# ------------------------------------------------------------------------------------ residual in streams
+def _f32_vec(t: Optional[torch.Tensor], n: int, op: str, name: str) -> None:
+    if t is None:
+        return
+    if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+        raise ShapeError(op, f"{name} must be contiguous float32 with {n} elements, got {t.dtype} {list(t.shape)}")
+
+
+@_timed
+def stream_norm(streams: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], out_coef: Optional[torch.Tensor],
+                in_coef: Optional[torch.Tensor], weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+    """The read of a residual kept as S streams, with the write that was still pending done first and
+    an RMS norm in `groups` groups behind it. streams float32 [T, S, W]. With `y` [T, W]: every stream
+    t becomes sum_s mix[s, t] * stream s + out_coef[t] * y (stored, unless `rows` is given: then the
+    rows are only looked at). Then u = sum_s in_coef[s] * stream s (all ones if None), each of the
+    `groups` consecutive parts of u divided by sqrt(mean(part^2) + eps), times weight.
+    out [R, copies, W] (or [R, W]) receives the result, `copies` times side by side."""
+    op = "stream_norm"
+    _cuda(op, streams, y, mix, out_coef, in_coef, weight, out, rows)
+    if streams.dtype != torch.float32 or streams.dim() != 3 or not streams.is_contiguous():
+        raise ShapeError(op, f"streams must be contiguous float32 [T, S, W], got {streams.dtype} {list(streams.shape)}")
+    T, S, W = streams.shape
+    if groups < 1 or W % groups != 0:
+        raise ShapeError(op, f"a width of {W} cannot be cut into {groups} equal groups")
+    if S > 8:
+        raise ShapeError(op, f"{S} streams: at most 8 are supported")
+    _f32_vec(weight, W, op, "weight")
+    _f32_vec(in_coef, S, op, "in_coef")
+    if y is not None:
+        if mix is None or out_coef is None:
+            raise ShapeError(op, "a pending write needs its mix and out coefficients")
+        _f32_vec(mix, S * S, op, "mix")
+        _f32_vec(out_coef, S, op, "out_coef")
+        if y.shape != (T, W) or not y.is_contiguous():
+            raise ShapeError(op, f"y must be contiguous [{T}, {W}], got {list(y.shape)}")
+    R = T
+    if rows is not None:
+        R = rows.numel()
+        _int32_vec(rows, R, op, "rows")
+    if not out.is_contiguous() or out.numel() % (R * W) != 0 or out.shape[0] != R or out.numel() == 0 and R:
+        raise ShapeError(op, f"out must be contiguous [{R}, copies, {W}], got {list(out.shape)}")
+    copies = out.numel() // (R * W) if R else 1
+    f = _fn("streams", "vob_stream_norm", [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P])
+    _check(f(_ptr(streams), _ptr(y), _code(y, op) if y is not None else 0, _ptr(mix), _ptr(out_coef), _ptr(in_coef), _ptr(weight),
+             _ptr(rows), _ptr(out), _code(out, op), R, S, W, int(groups), float(eps), copies, _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ linear recurrences
+@_timed
+def delta_prep(proj: torch.Tensor, k_off: int, a_off: int, low_off: int, rank: int, w2: torch.Tensor, w0: torch.Tensor,
+               a_bias: torch.Tensor, heads: int, dim: int, w_out: torch.Tensor, b_out: torch.Tensor, u_out: torch.Tensor) -> None:
+    """What the delta-rule recurrence reads besides r, k, v, per token, head and key channel, all float32
+    [T, heads * dim]: u = k / sqrt(sum k^2 + 1e-6) per head; b = sigmoid(a + a_bias) * u;
+    w = exp(-exp(-1/2) * sigmoid(w0 + w2 tanh(low))). k, a and low (width `rank`) are the columns
+    k_off.., a_off.., low_off.. of `proj` [T, ld]."""
+    op = "delta_prep"
+    _cuda(op, proj, w2, w0, a_bias, w_out, b_out, u_out)
+    _rows_2d(proj, op, "proj")
+    T, hd = proj.shape[0], heads * dim
+    if w2.shape != (hd, rank) or not w2.is_contiguous() or w2.dtype != proj.dtype:
+        raise ShapeError(op, f"w2 must be contiguous {proj.dtype} [{hd}, {rank}], got {w2.dtype} {list(w2.shape)}")
+    _f32_vec(w0, hd, op, "w0")
+    _f32_vec(a_bias, hd, op, "a_bias")
+    for name, t in (("w_out", w_out), ("b_out", b_out), ("u_out", u_out)):
+        if t.dtype != torch.float32 or t.shape != (T, hd) or not t.is_contiguous():
+            raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {hd}], got {t.dtype} {list(t.shape)}")
+    for off, n in ((k_off, hd), (a_off, hd), (low_off, rank)):
+        if off < 0 or off + n > proj.shape[1]:
+            raise ShapeError(op, f"columns {off}..{off + n} lie outside proj's {proj.shape[1]}")
+    f = _fn("recurrence", "vob_delta_prep", [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _P])
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), k_off, a_off, low_off, rank, _ptr(w2), _code(w2, op), _ptr(w0), _ptr(a_bias),
+             T, heads, dim, _ptr(w_out), _ptr(b_out), _ptr(u_out), _stream()), op)
+
+
+@_timed
+def rotate_scale(src: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, heads: int, dim: int, rot: int, scale: float,
+                 out: torch.Tensor) -> None:
+    """out float32 [T, heads * dim] = scale * (src with the first `rot` features of every head rotated by
+    position * inv_freq, feature i paired with i + rot / 2). src: [T, heads * dim] with any row stride."""
+    op = "rotate_scale"
+    _cuda(op, src, positions, inv_freq, out)
+    _rows_2d(src, op, "src")
+    T = src.shape[0]
+    if src.shape[1] != heads * dim or out.shape != (T, heads * dim) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise ShapeError(op, f"src [{T}, {heads * dim}] and a contiguous float32 out of the same shape are needed, got "
+                             f"{list(src.shape)} and {out.dtype} {list(out.shape)}")
+    if rot % 2 or rot > dim or rot < 0:
+        raise ShapeError(op, f"{rot} rotated features do not fit a head of {dim}")
+    _int32_vec(positions, T, op, "positions")
+    _f32_vec(inv_freq, rot // 2, op, "inv_freq")
+    f = _fn("recurrence", "vob_rotate_scale", [_P, _I, _L, _P, _P, _I, _I, _I, _I, _F, _P, _P])
+    _check(f(_ptr(src), _code(src, op), src.stride(0), _ptr(positions), _ptr(inv_freq), T, heads, dim, rot, float(scale), _ptr(out),
+             _stream()), op)
+
+
+@_timed
+def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
+                    u: Optional[torch.Tensor], state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor,
+                    num_seqs: int, heads: int, out: torch.Tensor) -> None:
+    """The recurrence over each request's rows of this step, from and to its state slot.
+    mode 0: S = diag(w_t) S - b_t (u_t^T S) + k_t v_t^T with w, b, u float32 [T, heads * K];
+    mode 1: S = w[h] S + k_t v_t^T with w float32 [heads]. o_t = S^T r_t -> out float32 [T, heads * V].
+    state float32 [slots, heads, K, V]; r, k [T, heads * K] and v [T, heads * V] with any row stride."""
+    op = "recurrence_scan"
+    _cuda(op, r, k, v, w, b, u, state, seq_starts, state_slots, out)
+    for name, t in (("r", r), ("k", k), ("v", v)):
+        _rows_2d(t, op, name)
+    if state.dtype != torch.float32 or state.dim() != 4 or not state.is_contiguous() or state.shape[1] != heads:
+        raise ShapeError(op, f"state must be contiguous float32 [slots, {heads}, K, V], got {state.dtype} {list(state.shape)}")
+    K, V = state.shape[2], state.shape[3]
+    T = r.shape[0]
+    if r.shape != (T, heads * K) or k.shape != (T, heads * K) or v.shape != (T, heads * V) or r.dtype != k.dtype:
+        raise ShapeError(op, f"r, k [{T}, {heads * K}] and v [{T}, {heads * V}] are needed, got {list(r.shape)}, {list(k.shape)}, {list(v.shape)}")
+    if out.shape != (T, heads * V) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous float32 [{T}, {heads * V}], got {out.dtype} {list(out.shape)}")
+    if mode == 0:
+        for name, t in (("w", w), ("b", b), ("u", u)):
+            if t is None or t.dtype != torch.float32 or t.shape != (T, heads * K) or not t.is_contiguous():
+                raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {heads * K}]")
+    elif mode == 1:
+        _f32_vec(w, heads, op, "w")
+    else:
+        raise ShapeError(op, f"mode {mode} is not known")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(state_slots, num_seqs, op, "state_slots")
+    f = _fn("recurrence", "vob_recurrence_scan", [_I, _P, _L, _P, _L, _I, _P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P])
+    _check(f(mode, _ptr(r), r.stride(0), _ptr(k), k.stride(0), _code(r, op), _ptr(v), v.stride(0), _code(v, op), _ptr(w), _ptr(b), _ptr(u),
+             _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), num_seqs, heads, K, V, _stream()), op)
+
+
+@_timed
+def recurrence_post(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], gate_mode: str, eps: float, heads: int,
+                    out: torch.Tensor) -> None:
+    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate), head by head; act is "sigmoid" or "silu".
+    o float32 [T, heads * V]; gate [T, heads * V] (any row stride) and out (contiguous) in the activations' type."""
+    op = "recurrence_post"
+    _cuda(op, o, gate, weight, out)
+    _rows_2d(gate, op, "gate")
+    T, hv = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or hv % heads != 0:
+        raise ShapeError(op, f"o must be contiguous float32 [T, heads * V], got {o.dtype} {list(o.shape)}")
+    if gate.shape != (T, hv) or out.shape != (T, hv) or out.dtype != gate.dtype or not out.is_contiguous():
+        raise ShapeError(op, f"gate and out must be [{T}, {hv}] of one type, got {list(gate.shape)} and {list(out.shape)}")
+    _f32_vec(weight, hv, op, "weight")
+    if gate_mode not in ("sigmoid", "silu"):
+        raise ShapeError(op, f"gate {gate_mode!r} is not known (sigmoid or silu)")
+    f = _fn("recurrence", "vob_recurrence_post", [_P, _P, _I, _L, _P, _I, _F, _I, _I, _I, _P, _P])
+    _check(f(_ptr(o), _ptr(gate), _code(gate, op), gate.stride(0), _ptr(weight), 1 if gate_mode == "silu" else 0, float(eps), T, heads,
+             hv // heads, _ptr(out), _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ attention over a latent cache
+@_timed
+def latent_prep(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int, down_off: int, rank: int, norm_w: torch.Tensor,
+                eps: float, positions: torch.Tensor, slots: Optional[torch.Tensor], inv_freq: torch.Tensor, lat: torch.Tensor,
+                kr: torch.Tensor, q_rot: torch.Tensor) -> None:
+    """Per token: the latent (first `rank` columns of the down projection, RMS norm with weight) and the
+    rotated key part (its last `rot` columns, rotary positions) go to the token's cache slot (lat
+    [pages, 1, page, rank], kr [pages, 1, page, rot]); the rotated query part of every head (the last
+    `rot` of its dim + rot columns) goes to q_rot float32 [T, heads, rot]."""
+    op = "latent_prep"
+    _cuda(op, proj, norm_w, positions, slots, inv_freq, lat, kr, q_rot)
+    _rows_2d(proj, op, "proj")
+    T = proj.shape[0]
+    if q_off < 0 or q_off + heads * (dim + rot) > proj.shape[1] or down_off < 0 or down_off + rank + rot > proj.shape[1]:
+        raise ShapeError(op, f"the query or down-projection columns lie outside proj's {proj.shape[1]}")
+    for name, t, w in (("lat", lat, rank), ("kr", kr, rot)):
+        if t.dim() != 4 or t.shape[1] != 1 or t.shape[3] != w or not t.is_contiguous() or t.dtype != proj.dtype:
+            raise ShapeError(op, f"{name} must be contiguous {proj.dtype} [pages, 1, page, {w}], got {t.dtype} {list(t.shape)}")
+    if q_rot.shape != (T, heads, rot) or q_rot.dtype != torch.float32 or not q_rot.is_contiguous():
+        raise ShapeError(op, f"q_rot must be contiguous float32 [{T}, {heads}, {rot}], got {q_rot.dtype} {list(q_rot.shape)}")
+    _f32_vec(norm_w, rank, op, "norm_w")
+    _f32_vec(inv_freq, rot // 2, op, "inv_freq")
+    _int32_vec(positions, T, op, "positions")
+    if slots is not None:
+        _int32_vec(slots, T, op, "slots")
+    f = _fn("latent_attention", "vob_latent_prep", [_P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _F, _P, _P, _P, _P, _P, _I, _P, _I, _P])
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), q_off, heads, dim, rot, down_off, rank, _ptr(norm_w), float(eps), _ptr(positions),
+             _ptr(slots), _ptr(inv_freq), _ptr(lat), _ptr(kr), _code(lat, op), _ptr(q_rot), T, _stream()), op)
+
+
+@_timed
+def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, kr: torch.Tensor, block_tables: torch.Tensor,
+                  row_seq: torch.Tensor, positions: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """Causal attention of every row over its request's latent pages: score = (q_lat . c + q_rot . kr) *
+    scale, softmax in float32, out_lat = sum of weights * c. q_lat float32 and out (cache type) are
+    indexed [T, heads, rank] through their strides (last stride 1); q_rot float32 [T, heads, rot]."""
+    op = "latent_attend"
+    _cuda(op, q_lat, q_rot, lat, kr, block_tables, row_seq, positions, out)
+    if q_lat.dim() != 3 or q_lat.dtype != torch.float32 or q_lat.stride(2) != 1:
+        raise ShapeError(op, f"q_lat must be float32 [T, heads, rank] with unit inner stride, got {q_lat.dtype} {list(q_lat.shape)}")
+    T, H, L = q_lat.shape
+    R = kr.shape[3]
+    if out.shape != (T, H, L) or out.stride(2) != 1 or out.dtype != lat.dtype:
+        raise ShapeError(op, f"out must be {lat.dtype} [{T}, {H}, {L}] with unit inner stride, got {out.dtype} {list(out.shape)}")
+    if q_rot.shape != (T, H, R) or q_rot.dtype != torch.float32 or not q_rot.is_contiguous():
+        raise ShapeError(op, f"q_rot must be contiguous float32 [{T}, {H}, {R}], got {q_rot.dtype} {list(q_rot.shape)}")
+    if lat.dim() != 4 or lat.shape[1] != 1 or lat.shape[3] != L or kr.shape[:3] != lat.shape[:3] or kr.dtype != lat.dtype \
+            or not lat.is_contiguous() or not kr.is_contiguous():
+        raise ShapeError(op, f"lat [pages, 1, page, {L}] and kr [pages, 1, page, {R}] of one type are needed, got {list(lat.shape)} and {list(kr.shape)}")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, "block_tables must be contiguous int32 [requests, max_pages]")
+    _int32_vec(row_seq, T, op, "row_seq")
+    _int32_vec(positions, T, op, "positions")
+    f = _fn("latent_attention", "vob_latent_attend", [_P, _L, _L, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _L, _L, _P])
+    _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _code(lat, op), _ptr(block_tables),
+             block_tables.shape[1], _ptr(row_seq), _ptr(positions), lat.shape[2], T, H, L, R, float(scale), _ptr(out), _code(out, op),
+             out.stride(0), out.stride(1), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention

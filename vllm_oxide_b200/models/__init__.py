@@ -1,4 +1,5 @@
 """Architectures this engine knows. Importing the package registers them."""
 from .llama import LLAMA, BuildContext, build_llama, llama_manifest
+from .rotepel import ROTEPEL, build_rotepel, rotepel_manifest
 
-__all__ = ["LLAMA", "BuildContext", "build_llama", "llama_manifest"]
+__all__ = ["LLAMA", "BuildContext", "build_llama", "llama_manifest", "ROTEPEL", "build_rotepel", "rotepel_manifest"]

@@ -6,7 +6,11 @@ from .attention import Attention
 from .swiglu import SwiGLU
 from .embedding import Embedding, LMHead
 from .block import Block
+from .streams import PendingWrite, StreamBlock, StreamCoefficients, StreamEmbedding, StreamNorm
+from .recurrent import GeneralDelta, Retention
+from .latent_attention import LatentAttention
 
 __all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
            "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
-           "SwiGLU", "Embedding", "LMHead", "Block"]
+           "SwiGLU", "Embedding", "LMHead", "Block", "PendingWrite", "StreamBlock", "StreamCoefficients", "StreamEmbedding",
+           "StreamNorm", "GeneralDelta", "Retention", "LatentAttention"]

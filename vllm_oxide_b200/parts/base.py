@@ -276,3 +276,4 @@ class ModelSpec:
     max_position: Optional[int] = None  # longest position the position encodings allow
     eos_token_ids: Tuple[int, ...] = ()
     weight_bytes: int = 0               # bytes a decode step must read of the weights
+    residual_streams: int = 1           # the residual is float32 [rows, residual_streams * hidden_size]

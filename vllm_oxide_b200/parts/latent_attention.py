@@ -1,0 +1,94 @@
+"""Attention whose cache holds one small latent vector per token instead of keys and values per head.
+
+    q = W_q h, head by head [dim plain features | rot_dim rotated features]
+    W_dkv h = [kv_rank columns | rot_dim columns];  c = RMSNorm(first kv_rank, weight);  kr = rotary(last rot_dim)
+    key of head n = [W_uk,n c | kr],  value of head n = W_uv,n c
+    score = (q_plain . k_plain + q_rot . kr) * scale,  causal, ordinary softmax;  out = W_o concat(heads)
+
+Only c and kr are cached (`CacheSpec.tensors`: two tensors with one "head" each), and no key or value
+is ever built from them. Since k_plain = W_uk,n c, the plain part of the score is (W_uk,n^T q_plain) . c:
+the query is taken into the latent space once per row (a product per head), the attention kernel
+works on c directly and returns sum_j p_j c_j, and W_uv,n is applied to that (softmax weights
+sum to one, so W_uv (sum_j p_j c_j) = sum_j p_j W_uv c_j). A cached token costs kv_rank + rot_dim
+elements whatever the number of heads, and a decode step reads each of them once for all heads.
+Scores, softmax and the rotation are float32; the query in the latent space stays float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from .base import CacheSpec, LayerCache, Mixer, PagedTensorSpec, StepContext, aligned
+from .linear import matmul, to_compute
+from .rotary import rotary_inv_freq
+
+
+class LatentAttention(Mixer):
+    def __init__(self, wq, wdkv, dkv_norm, wuk, wuv, wo, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
+                 rot_base: float, eps: float, dtype=torch.bfloat16, device="cuda"):
+        self.H, self.D, self.R, self.V, self.L = int(heads), int(dim), int(rot_dim), int(vdim), int(kv_rank)
+        H, D, R, V, L = self.H, self.D, self.R, self.V, self.L
+        hidden = wq.shape[1]
+        if wq.shape != (H * (D + R), hidden) or wdkv.shape != (L + R, hidden) or wuk.shape != (H * D, L) or wuv.shape != (H * V, L) \
+                or wo.shape != (hidden, H * V) or dkv_norm.shape != (L,):
+            raise ValueError(f"projection shapes do not fit {H} heads of {D}+{R} / {V} with a latent of {L} over a width of {hidden}")
+        if R % 2 or R <= 0:
+            raise ValueError(f"the rotated part must have an even, positive size, got {R}")
+        self.w_in = to_compute(torch.cat([wq, wdkv], dim=0), dtype, device)
+        # per head, as `linear` wants its weights ([out, in]): latent <- plain query features, values <- latent
+        self.w_qlat = to_compute(wuk.reshape(H, D, L).transpose(1, 2), dtype, device)          # [H, L, D]
+        self.w_val = to_compute(wuv.reshape(H, V, L), dtype, device)                            # [H, V, L]
+        self.w_o = to_compute(wo, dtype, device)
+        self.norm_weight = dkv_norm.to(device=device, dtype=torch.float32).contiguous()
+        self.inv_freq = torch.from_numpy(rotary_inv_freq(R, rot_base).copy()).to(device)
+        self.scale, self.eps, self.hidden, self.dtype = float(scale), float(eps), hidden, dtype
+        self.batched = True       # bfloat16: the per-head products as one batched library product (False: one by one, tests)
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return CacheSpec(kind="full", tensors=(PagedTensorSpec(1, self.L), PagedTensorSpec(1, self.R)))
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_qlat.numel() + self.w_val.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def workspace_bytes(self, rows: int) -> int:
+        es, H = self.w_in.element_size(), self.H
+        return (aligned(rows * self.w_in.shape[0] * es) + aligned(rows * H * self.R * 4) + aligned(rows * H * self.L * 4)
+                + aligned(rows * H * self.L * es) + 2 * aligned(rows * H * self.V * es))
+
+    def kernel_modules(self, dtype, max_rows):
+        return ("gemm_f32", "latent_attention") if dtype == torch.float32 else ("gemm_sm100", "latent_attention")
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
+        if cache is None:
+            raise ValueError("latent attention needs a cache")
+        H, D, R, V, L = self.H, self.D, self.R, self.V, self.L
+        T = x.shape[0]
+        lat, kr = cache.tensors
+        proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
+        q_rot = ctx.alloc((T, H, R), torch.float32)
+        kernels.latent_prep(proj, 0, H, D, R, H * (D + R), L, self.norm_weight, self.eps, ctx.positions,
+                            ctx.slot_mapping[cache.group] if cache.write else None, self.inv_freq, lat, kr, q_rot)
+        q_heads = proj[:, :H * (D + R)].view(T, H, D + R)[:, :, :D]                 # [T, H, D], strided
+        bt = ctx.block_tables[cache.group]
+        if self.dtype == torch.bfloat16 and self.batched:
+            # head-major buffers, so that each of the two per-head products is one batched product
+            q_lat = ctx.alloc((H, T, L), torch.float32)
+            torch.bmm(q_heads.transpose(0, 1), self.w_qlat.transpose(1, 2), out_dtype=torch.float32, out=q_lat)
+            out_lat = ctx.alloc((H, T, L))
+            kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat.transpose(0, 1))
+            vals = ctx.alloc((H, T, V))
+            torch.bmm(out_lat, self.w_val.transpose(1, 2), out=vals)
+            attn = ctx.alloc((T, H * V))
+            attn.view(T, H, V).copy_(vals.transpose(0, 1))
+        else:
+            q_lat = ctx.alloc((T, H, L), torch.float32)
+            for h in range(H):
+                kernels.linear(q_heads[:, h], self.w_qlat[h], q_lat[:, h])
+            out_lat = ctx.alloc((T, H, L))
+            kernels.latent_attend(q_lat, q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat)
+            attn = ctx.alloc((T, H * V))
+            for h in range(H):
+                kernels.linear(out_lat[:, h], self.w_val[h], attn[:, h * V:(h + 1) * V])
+        return matmul(attn, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))

@@ -1,0 +1,132 @@
+"""Mixers whose memory is a matrix state per request and head instead of a cache of keys: the state
+S [key channels, value channels] is float32, lives in the request's state slot (`StateSpec`), starts
+at zero when the request is admitted and is carried from token to token across steps.
+
+`GeneralDelta`, the generalized delta rule, per head (all of size `dim`):
+    r, k, v = W_r h, W_k h, W_v h;   u = k / sqrt(sum k^2 + 1e-6)
+    w = exp(-exp(-1/2) sigmoid(W_w2 tanh(W_w1 h) + w0))     decay per key channel
+    a = sigmoid(W_a h + a_bias)                              removal rate per key channel
+    S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T;   o = S_t^T r
+    out = W_o (rms_head(o) * norm_weight * sigmoid(W_g h))
+
+`Retention`, linear attention with a fixed decay per head, no softmax and no denominator:
+    q, k = rotary(W_q h), rotary(W_k h) * dim^-1/2;   v = W_v h  (heads of `vdim`)
+    S_t = decay_h S_(t-1) + k v^T;   o = S_t^T q;   out = W_o (rms_head(o) * silu(W_g h))
+
+Both run the same scan kernel (`kernels.recurrence_scan`) for prompt portions and single tokens
+alike. The projections are one matrix product each side of it, in the compute dtype; everything
+between them that enters the recurrence (unit key, decay, removal rate, rotation, the state, the
+per-head norm and the gates) is float32.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .. import kernels
+from .base import LayerCache, Mixer, StateSpec, StepContext, aligned
+from .linear import matmul, to_compute
+from .rotary import rotary_inv_freq
+
+
+def _modules(dtype):
+    return ("gemm_f32", "recurrence") if dtype == torch.float32 else ("gemm_sm100", "recurrence")
+
+
+class GeneralDelta(Mixer):
+    def __init__(self, wr, wk, wv, wa, a_bias, wg, w1, w2, w0, norm_weight, wo, heads: int, dim: int, eps: float,
+                 dtype=torch.bfloat16, device="cuda"):
+        self.H, self.D = int(heads), int(dim)
+        hd, hidden = self.H * self.D, wr.shape[1]
+        for name, t in (("r", wr), ("k", wk), ("v", wv), ("a", wa), ("g", wg)):
+            if t.shape != (hd, hidden):
+                raise ValueError(f"projection '{name}' is {list(t.shape)}, {self.H} heads of {self.D} over a width of {hidden} need [{hd}, {hidden}]")
+        self.rank = w1.shape[0]
+        if w1.shape != (self.rank, hidden) or w2.shape != (hd, self.rank) or wo.shape != (hidden, hd):
+            raise ValueError(f"decay projection {list(w1.shape)} / {list(w2.shape)} or output projection {list(wo.shape)} do not fit")
+        for name, t in (("a_bias", a_bias), ("w0", w0), ("norm", norm_weight)):
+            if t.shape != (hd,):
+                raise ValueError(f"'{name}' must have {hd} entries, got {list(t.shape)}")
+        # one matrix [Wr; Wk; Wv; Wa; Wg; Ww1]: a single product gives every projection of the input
+        self.w_in = to_compute(torch.cat([wr, wk, wv, wa, wg, w1], dim=0), dtype, device)
+        self.w2 = to_compute(w2, dtype, device)
+        self.w_o = to_compute(wo, dtype, device)
+        f32 = dict(device=device, dtype=torch.float32)
+        self.a_bias, self.w0, self.norm_weight = a_bias.to(**f32).contiguous(), w0.to(**f32).contiguous(), norm_weight.to(**f32).contiguous()
+        self.eps, self.hidden, self.dtype = float(eps), hidden, dtype
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((self.H, self.D, self.D), torch.float32)
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w2.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def workspace_bytes(self, rows: int) -> int:
+        es, hd = self.w_in.element_size(), self.H * self.D
+        return aligned(rows * self.w_in.shape[0] * es) + 4 * aligned(rows * hd * 4) + aligned(rows * hd * es)
+
+    def kernel_modules(self, dtype, max_rows):
+        return _modules(dtype)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state: Optional[torch.Tensor], out=None) -> torch.Tensor:
+        if state is None:
+            raise ValueError("the delta rule needs its state")
+        T, hd = x.shape[0], self.H * self.D
+        proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
+        w, b, u, o = (ctx.alloc((T, hd), torch.float32) for _ in range(4))
+        kernels.delta_prep(proj, hd, 3 * hd, 5 * hd, self.rank, self.w2, self.w0, self.a_bias, self.H, self.D, w, b, u)
+        kernels.recurrence_scan(0, proj[:, :hd], proj[:, hd:2 * hd], proj[:, 2 * hd:3 * hd], w, b, u, state, ctx.seq_starts,
+                                ctx.state_slots, ctx.seqs, self.H, o)
+        gated = ctx.alloc((T, hd))
+        kernels.recurrence_post(o, proj[:, 4 * hd:5 * hd], self.norm_weight, "sigmoid", self.eps, self.H, gated)
+        return matmul(gated, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
+
+
+class Retention(Mixer):
+    def __init__(self, wq, wk, wv, wg, wo, heads: int, dim: int, vdim: int, decay: Sequence[float], rot_dims: int, rot_base: float,
+                 eps: float, dtype=torch.bfloat16, device="cuda"):
+        self.H, self.D, self.V = int(heads), int(dim), int(vdim)
+        hk, hv, hidden = self.H * self.D, self.H * self.V, wq.shape[1]
+        if wq.shape != (hk, hidden) or wk.shape != (hk, hidden) or wv.shape != (hv, hidden) or wg.shape != (hv, hidden) or wo.shape != (hidden, hv):
+            raise ValueError(f"projection shapes do not fit {self.H} heads of {self.D} / {self.V} over a width of {hidden}")
+        if len(decay) != self.H:
+            raise ValueError(f"{len(decay)} decays for {self.H} heads")
+        if rot_dims % 2 or not 0 <= rot_dims <= self.D:
+            raise ValueError(f"{rot_dims} rotated features do not fit a head of {self.D}")
+        self.w_in = to_compute(torch.cat([wq, wk, wv, wg], dim=0), dtype, device)
+        self.w_o = to_compute(wo, dtype, device)
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32, device=device)
+        self.rot = int(rot_dims)
+        self.inv_freq = torch.from_numpy(rotary_inv_freq(self.rot, rot_base).copy()).to(device) if self.rot else \
+            torch.zeros(0, dtype=torch.float32, device=device)
+        self.k_scale = float(self.D) ** -0.5
+        self.eps, self.hidden, self.dtype = float(eps), hidden, dtype
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((self.H, self.D, self.V), torch.float32)
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def workspace_bytes(self, rows: int) -> int:
+        es, hk, hv = self.w_in.element_size(), self.H * self.D, self.H * self.V
+        return aligned(rows * self.w_in.shape[0] * es) + 2 * aligned(rows * hk * 4) + aligned(rows * hv * 4) + aligned(rows * hv * es)
+
+    def kernel_modules(self, dtype, max_rows):
+        return _modules(dtype)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state: Optional[torch.Tensor], out=None) -> torch.Tensor:
+        if state is None:
+            raise ValueError("retention needs its state")
+        T, hk, hv = x.shape[0], self.H * self.D, self.H * self.V
+        proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
+        q, k = ctx.alloc((T, hk), torch.float32), ctx.alloc((T, hk), torch.float32)
+        kernels.rotate_scale(proj[:, :hk], ctx.positions, self.inv_freq, self.H, self.D, self.rot, 1.0, q)
+        kernels.rotate_scale(proj[:, hk:2 * hk], ctx.positions, self.inv_freq, self.H, self.D, self.rot, self.k_scale, k)
+        o = ctx.alloc((T, hv), torch.float32)
+        kernels.recurrence_scan(1, q, k, proj[:, 2 * hk:2 * hk + hv], self.decay, None, None, state, ctx.seq_starts, ctx.state_slots,
+                                ctx.seqs, self.H, o)
+        gated = ctx.alloc((T, hv))
+        kernels.recurrence_post(o, proj[:, 2 * hk + hv:], None, "silu", self.eps, self.H, gated)
+        return matmul(gated, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))

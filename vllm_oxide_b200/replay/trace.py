@@ -75,6 +75,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time; the cache pool is made for this many")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-seqs", type=int, default=4, help="requests that may be live at once (state slots)")
     args = ap.parse_args(argv)
 
     from ..config import EngineConfig
@@ -84,7 +85,7 @@ def main(argv=None) -> int:
     page = args.page_size
     num_pages = max(1, -(-args.max_tokens // page))
     cap = num_pages * page
-    engine = EngineConfig(max_batch_tokens=cap, max_seqs=8, max_model_len=cap, block_size=page,
+    engine = EngineConfig(max_batch_tokens=cap, max_seqs=args.max_seqs, max_model_len=cap, block_size=page,
                           num_pages=num_pages, dtype=args.dtype, cuda_graphs=False)
     print(f"[trace_run] loading {args.model} ({args.dtype}); kernels are compiled at the first call",
           file=sys.stderr, flush=True)

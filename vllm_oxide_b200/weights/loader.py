@@ -28,7 +28,8 @@ _INT_NAMES = ("I8", "U8", "I16", "I32", "I64")
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """What the model expects under one name."""
+    """What the model expects under one name. A dimension of -1 is not fixed by the configuration:
+    whatever the stored tensor has there is taken (such a tensor cannot be drawn at random)."""
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" or "int"
     init: str = "normal"         # random-weights rule: "normal", "ones" or "zeros"
@@ -82,7 +83,7 @@ def check_against_manifest(source: str, found: Mapping[str, Tuple[Tuple[int, ...
         if n not in found:
             continue
         shape, dt = found[n]
-        if tuple(shape) != tuple(spec.shape):
+        if len(shape) != len(spec.shape) or any(want != -1 and want != got for want, got in zip(spec.shape, shape)):
             wrong_shape.append((n, tuple(spec.shape), tuple(shape)))
         ok = _FLOAT_NAMES if spec.kind == "float" else _INT_NAMES
         if dt not in ok:

@@ -30,6 +30,9 @@ def random_tensors(manifest: Mapping[str, TensorSpec], seed: int, std: float = 0
     so that a test notices a norm weight that is ignored or misapplied."""
     out = {}
     for name, spec in manifest.items():
+        if any(n < 0 for n in spec.shape):
+            raise ValueError(f"tensor {name!r}: a dimension is left to the stored tensor {tuple(spec.shape)}; "
+                             "the configuration must state it before weights can be drawn")
         g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, name))
         if spec.kind == "int":
