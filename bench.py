@@ -621,6 +621,186 @@ def timeline_of_a_decode_step(llm, prompts, B, prompt_len, gen_len):
 
 
 # ------------------------------------------------------------------------------------------------ main
+# ------------------------------------------------------------------------------------------------ Rotepel beside Llama
+# Layer sizes at which the Rotepel design is measured beside the Llama decoder of the same width, feed-forward
+# and layer count: per size the three mixers' heads and sizes (delta rule, retention, latent attention).
+ROTEPEL_SIZES = {
+    "1b": dict(llama="1b", width=2048, ff=8192, delta=dict(heads=32, dim=64, decay_rank=64),
+               retention=dict(heads=16, dim=128, vdim=128), latent=dict(heads=32, dim=64, rot_dim=32, vdim=64, kv_rank=256)),
+    "3b": dict(llama="3b", width=3072, ff=8192, delta=dict(heads=24, dim=128, decay_rank=96),
+               retention=dict(heads=12, dim=128, vdim=256), latent=dict(heads=24, dim=128, rot_dim=64, vdim=128, kv_rank=512)),
+}
+
+
+def make_rotepel_engine(rs, blocks, max_seqs, tokens_per_request, context):
+    """(config, LLM): `blocks` times the four layers [delta rule, retention, delta rule, latent attention], two streams,
+    two norm groups, random weights drawn on the device."""
+    import torch
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import EngineConfig, RotepelConfig, RotepelLayer
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    d, r, l = rs["delta"], rs["retention"], rs["latent"]
+    delta = RotepelLayer(type="general_delta", ff=rs["ff"], **d)
+    ret = RotepelLayer(type="retention", ff=rs["ff"], decay=tuple(1.0 - 2.0 ** -(5 + i % 6) for i in range(r["heads"])),
+                       rot_dims=r["dim"], rot_base=1e6, **r)
+    lat = RotepelLayer(type="latent_attention", ff=rs["ff"], scale=(l["dim"] + l["rot_dim"]) ** -0.5, rot_dims=l["rot_dim"],
+                       rot_base=5e5, **l)
+    cfg = RotepelConfig(vocab=128256, width=rs["width"], layers=(delta, ret, delta, lat) * blocks, norm_eps=1e-5, norm_groups=2, streams=2)
+    pages_per_req = -(-(tokens_per_request + 16) // 16)
+    fields = dict(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
+                  num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=True)
+    fields.update(ENGINE_OVERRIDES)
+    tensors = random_tensors(models.rotepel_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    runner = ModelRunner(cfg, tensors, EngineConfig(**fields))
+    del tensors
+    return cfg, LLM(runner)
+
+
+def op_profile(llm, tokens, n, batch):
+    """Device time op by op (CUDA events around every kernel wrapper, launches one by one) of one step of `n` prompt
+    tokens and of one decode step of `batch` requests behind prompts of `n` tokens. Returns two lists of (op, calls, ms)."""
+    import torch
+    from vllm_oxide_b200 import kernels
+    runner, rt = llm.runner, llm.runner.rt
+    graphs, runner.graphs_enabled = runner.graphs_enabled, False
+    ids = list(range(800000, 800000 + batch))
+    try:
+        for i, rid in enumerate(ids):
+            runner.admit(rid)
+            runner.manager.reserve(rid, n)
+            arrays = runner.build_arrays([rt.StepEntry(rid, tokens[i][:n], [n - 1])])
+            if i == batch - 1:
+                with kernels.OpProfile() as prof:
+                    runner.step(arrays)
+                prefill = prof.totals()
+            else:
+                runner.step(arrays)
+            runner.manager.commit(rid, n)
+        decode = None
+        for rep in range(3):
+            for rid in ids:
+                runner.manager.reserve(rid, 1)
+            arrays = runner.build_arrays([rt.StepEntry(rid, [7], [0]) for rid in ids])
+            if rep == 2:
+                with kernels.OpProfile() as prof:
+                    runner.step(arrays)
+                decode = prof.totals()
+            else:
+                runner.step(arrays)
+            for rid in ids:
+                runner.manager.commit(rid, 1)
+        torch.cuda.synchronize()
+    finally:
+        for rid in ids:
+            runner.manager.release(rid)
+        runner.graphs_enabled = graphs
+    return prefill, decode
+
+
+def rotepel_roofline(rs, blocks, n, batch, peaks, prefill, decode):
+    """The new design's own kernels against their rooflines: algorithmic bytes (or FLOPs) of all their launches in one
+    step over the measured time, as a fraction of the measured copy bandwidth (or the measured bfloat16 product rate)."""
+    d, r, l = rs["delta"], rs["retention"], rs["latent"]
+    W, S = rs["width"], 2
+    norms = blocks * 4 * 2 + 1                       # two sublayers per layer, and the final norm (one row per request)
+    out = {}
+
+    def add(name, phase, totals, nbytes=None, flops=None):
+        ms = sum(t for op, _, t in totals if op == name)
+        if ms <= 0:
+            return
+        e = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["of_measured_hbm"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 2)
+            e["of_measured_bf16"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        out[f"{phase}:{name}"] = e
+    for phase, rows, totals in (("prefill", n, prefill), ("decode", batch, decode)):
+        # read and write S streams of float32, read the sublayer's output, write the normed row
+        add("stream_norm", phase, totals, nbytes=norms * rows * W * (2 * S * 4 + 2 + 2))
+        seqs = 1 if phase == "prefill" else batch
+        state = blocks * (2 * d["heads"] * d["dim"] * d["dim"] + r["heads"] * r["dim"] * r["vdim"]) * 4 * 2 * seqs
+        per_token = blocks * (2 * d["heads"] * d["dim"] * (3 * 2 + 3 * 4 + 4) + r["heads"] * (2 * r["dim"] * 4 + r["vdim"] * (2 + 4)))
+        # FLOPs of the recurrences as they are written (delta rule: 4 passes over K x V per token, retention 2)
+        fl = blocks * rows * 2 * (2 * d["heads"] * d["dim"] * d["dim"] * 4 + r["heads"] * r["dim"] * r["vdim"] * 2)
+        add("recurrence_scan", phase, totals, nbytes=state + rows * per_token, flops=fl)
+        keys = rows * (n + 1) / 2 if phase == "prefill" else batch * (n + 3)
+        add("latent_attend", phase, totals, nbytes=(blocks * batch * (n + 3) * (l["kv_rank"] + l["rot_dim"]) * 2) if phase == "decode" else None,
+            flops=blocks * keys * l["heads"] * 2 * (2 * l["kv_rank"] + l["rot_dim"]))
+    return out
+
+
+def llama_roofline(cfg, layers, n, batch, peaks, prefill, decode):
+    """The like kernels of the Llama decoder, the same way: the norm with the residual add, attention over the cache."""
+    out = {}
+    h, q, kv = cfg.hidden_size, cfg.q_dim, cfg.kv_dim
+
+    def add(names, label, phase, totals, nbytes=None, flops=None):
+        ms = sum(t for op, _, t in totals if op in names)
+        if ms <= 0:
+            return
+        e = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["of_measured_hbm"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 2)
+            e["of_measured_bf16"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        out[f"{phase}:{label}"] = e
+    for phase, rows, totals in (("prefill", n, prefill), ("decode", batch, decode)):
+        add(("add_rmsnorm",), "add_rmsnorm", phase, totals, nbytes=(2 * layers + 1) * rows * h * (2 * 4 + 2 + 2))
+        keys = rows * (n + 1) / 2 if phase == "prefill" else batch * (n + 3)
+        add(("attn_prefill_sm100", "attn_prefill_mma", "attn_decode_mma", "paged_attention"), "attention", phase, totals,
+            nbytes=layers * batch * (n + 3) * 2 * kv * 2 if phase == "decode" else None, flops=layers * keys * 4 * q)
+    return out
+
+
+def rotepel_compare(a):
+    """Prefill and decode of the Rotepel design beside the Llama decoder of the same width, feed-forward and number of
+    layers; one JSON line. Device-timed like the benchmark's own points: one step of 2,048 prompt tokens (median of 5
+    after 3), decode steps replayed from CUDA graphs (`--steps` steps a region, median region)."""
+    import torch
+    peaks = load_peaks()
+    n, B, blocks = 2048, a.batch, 2
+    gen = a.warmup + max(a.steps, MAX_TIMED_STEPS) + 64
+    sampler = ClockSampler()
+    sampler.start()
+    points = []
+    for key in a.rotepel.split(","):
+        rs = ROTEPEL_SIZES[key]
+        point = {"sizes": key, "layers": 4 * blocks, "prompt_len": n, "batch": B}
+        for arch in ("rotepel", "llama"):
+            if arch == "rotepel":
+                cfg, llm = make_rotepel_engine(rs, blocks, B, n + gen, 8192)
+                vocab = cfg.vocab
+            else:
+                cfg, llm = make_engine(SIZES[rs["llama"]], 4 * blocks, B, n + gen, 8192)
+                vocab = cfg.vocab_size
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for _ in range(B)]
+            ms_prefill = timed_prefill(llm, prompts[0], n)
+            ms_step, ctx_tokens, launches, regions = decode_device(llm, prompts, B, a.steps, a.warmup, n, gen)
+            prefill, decode = op_profile(llm, prompts, n, B)
+            e = {"prefill_tok_s": round(n / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                 "decode_tok_s": round(B / ms_step * 1e3, 1), "decode_ms_per_step": round(ms_step, 4),
+                 "decode_hbm_frac_of_measured": round(llm.runner.step_read_bytes(int(ctx_tokens)) / ms_step / 1e6 / peaks["hbm_gbs"], 3),
+                 "launches_per_decode_step": launches // a.steps,
+                 "ops_prefill_ms": {op: round(t, 4) for op, _, t in prefill}, "ops_decode_ms": {op: round(t, 4) for op, _, t in decode}}
+            e["kernels"] = rotepel_roofline(rs, blocks, n, B, peaks, prefill, decode) if arch == "rotepel" else \
+                llama_roofline(cfg, 4 * blocks, n, B, peaks, prefill, decode)
+            point[arch] = e
+            free_engine(llm)
+            del llm
+        points.append(point)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "Rotepel beside Llama at equal width, feed-forward and layer count: prefill and decode tok/s",
+                      "dtype": "bf16", "data": "synthetic", "peaks": peaks, "points": points, "clocks": clocks, "run": run_record()}))
+    return 0
+
+
 def main():
     if "--kernel" in sys.argv[1:]:
         return kernel_case(sys.argv[1:])
@@ -647,6 +827,9 @@ def main():
     ap.add_argument("--serve-min", type=int, default=128)
     ap.add_argument("--serve-max", type=int, default=4096)
     ap.add_argument("--timeline", action="store_true", help="per-kernel times of one decode step (VOB_TIMELINE=1 build)")
+    ap.add_argument("--rotepel", default=None, metavar="SIZES", const="1b,3b", nargs="?",
+                    help="instead of the benchmark's line: the Rotepel design beside Llama at equal sizes (1b, 3b or both), "
+                         "prefill and decode, with the time and roofline fraction of every kernel")
     ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
                     help="set a field of vllm_oxide_b200.tuning.TUNING (experiments)")
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
@@ -665,6 +848,8 @@ def main():
         return 2
     a.warmup = max(a.warmup, 3)
     a.steps = max(a.steps, 1)
+    if a.rotepel:
+        return rotepel_compare(a)
     prompt_len, gen_len = a.prompt_len, a.gen_len
     max_b = max(a.batch, 1 if (a.no_points or a.serve or a.timeline) else 64)
     if a.serve:

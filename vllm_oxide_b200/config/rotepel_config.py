@@ -162,6 +162,16 @@ class RotepelConfig:
         a, b, times = self.loop
         return tuple(range(a)) + tuple(range(a, b)) * times + tuple(range(b, n))
 
+    def param_count(self) -> int:
+        from ..models.rotepel import rotepel_manifest
+        total = 0
+        for spec in rotepel_manifest(self).values():
+            n = 1
+            for x in spec.shape:
+                n *= max(int(x), 0)
+            total += n
+        return total
+
     def to_dict(self) -> dict:
         d = {"architecture": NAME, "vocab": self.vocab, "width": self.width,
              "norm": {"eps": self.norm_eps, "groups": self.norm_groups},

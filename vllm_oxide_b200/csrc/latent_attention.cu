@@ -12,7 +12,9 @@
 // vob_latent_attend: scores, softmax weights and the weighted sum in float32, keys in page order
 // from the first, in tiles staged in shared memory; one warp per head, a block takes up to 8 heads
 // of one row, so a key tile is read once for all of them. The order of every sum depends only on the row's
-// position, never on how the request was cut into steps or on the batch around it.
+// position, never on how the request was cut into steps or on the batch around it. Steps of few rows
+// (single tokens) share a row's keys over `splits` blocks, whose partial results a second small kernel
+// puts together in a fixed order.
 #include "common.cuh"
 #include <math.h>
 VOB_PDL_SWITCH(latent_attention)
@@ -87,11 +89,11 @@ VOB_EXPORT int vob_latent_prep(const void* proj, int code, long ld, int q_off, i
 // TO, element (t, h, i) at t * o_ts + h * o_hs + i. NL = ceil(L / 32) registers per lane for q_lat and
 // for the weighted sum. Grid (rows, ceil(H / warps)); a block has `warps` warps, one head each.
 template <int NL, typename TC, typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                      const TC* __restrict__ lat, const TC* __restrict__ kr, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ row_seq, const int* __restrict__ positions, int page_size, int H, int L, int R,
-                     float scale, int KT, TO* __restrict__ out, long o_ts, long o_hs) {
+                     float scale, int KT, TO* __restrict__ out, long o_ts, long o_hs, int splits, float* __restrict__ part) {
     pdl_launch_dependents();
     pdl_wait(46);
     extern __shared__ float tile[];                 // [KT][L + R]
@@ -101,9 +103,13 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
     const bool head = h < H;
     const int pos = positions[t];
     TO* orow = out + (size_t)t * o_ts + (size_t)(head ? h : 0) * o_hs;
+    // with splits > 1 block z takes the z-th share of the row's keys and leaves (max, sum, weighted sum) in `part`
+    // [T, H, splits, L + 2]; the shares depend on the row's position and `splits` only
+    float* prow = part + (((size_t)t * H + (head ? h : 0)) * splits + blockIdx.z) * (L + 2);
     if (pos < 0) {
-        if (head)
+        if (head && splits == 1)
             for (int i = lane; i < L; i += 32) st_f(orow + i, 0.f);
+        if (head && splits > 1 && lane == 0) { prow[0] = -INFINITY; prow[1] = 0.f; }
         return;
     }
     const int* table = block_tables + (size_t)row_seq[t] * max_pages;
@@ -121,8 +127,9 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
         qr[i] = (head && c < R) ? q_rot[((size_t)t * H + h) * R + c] : 0.f;
     }
     float m = -INFINITY, l = 0.f;
-    const int nkeys = pos + 1;
-    for (int k0 = 0; k0 < nkeys; k0 += KT) {
+    const int share = ((pos + splits) / splits + KT - 1) / KT * KT;      // keys per block, whole tiles
+    const int nkeys = min(pos + 1, (int)(blockIdx.z + 1) * share);
+    for (int k0 = blockIdx.z * share; k0 < nkeys; k0 += KT) {
         const int n = min(KT, nkeys - k0);
         __syncthreads();
         for (int e = threadIdx.x; e < n * W; e += blockDim.x) {
@@ -158,7 +165,7 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
             m = mn;
         }
     }
-    if (head) {
+    if (head && splits == 1) {
         const float inv = 1.0f / l;
 #pragma unroll
         for (int i = 0; i < NL; ++i) {
@@ -166,35 +173,79 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
             if (c < L) st_f(orow + c, acc[i] * inv);
         }
     }
+    if (head && splits > 1) {
+        if (lane == 0) { prow[0] = m; prow[1] = l; }
+#pragma unroll
+        for (int i = 0; i < NL; ++i) {
+            const int c = lane + 32 * i;
+            if (c < L) prow[2 + c] = acc[i];
+        }
+    }
+}
+
+// The shares of a row's keys put together, in share order: out = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M).
+// Launch: one warp per (row, head).
+template <typename TO>
+__global__ void __launch_bounds__(32)
+latent_merge_kernel(const float* __restrict__ part, const int* __restrict__ positions, int H, int L, int splits,
+                    TO* __restrict__ out, long o_ts, long o_hs) {
+    pdl_launch_dependents();
+    pdl_wait(47);
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    TO* orow = out + (size_t)t * o_ts + (size_t)h * o_hs;
+    const float* p = part + ((size_t)t * H + h) * splits * (L + 2);
+    if (positions[t] < 0) {
+        for (int i = lane; i < L; i += 32) st_f(orow + i, 0.f);
+        return;
+    }
+    float M = -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (L + 2)]);
+    float l = 0.f;
+    for (int z = 0; z < splits; ++z) l = fmaf(p[(size_t)z * (L + 2) + 1], expf(p[(size_t)z * (L + 2)] - M), l);
+    const float inv = 1.0f / l;
+    for (int i = lane; i < L; i += 32) {
+        float a = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float* pz = p + (size_t)z * (L + 2);
+            if (pz[1] > 0.f) a = fmaf(pz[2 + i], expf(pz[0] - M), a);
+        }
+        st_f(orow + i, a * inv);
+    }
 }
 
 VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const float* q_rot, const void* lat, const void* kr,
                                  int cache_code, const int* block_tables, int max_pages, const int* row_seq, const int* positions,
                                  int page_size, int T, int H, int L, int R, float scale, void* out, int out_code, long o_ts, long o_hs,
-                                 cudaStream_t stream) {
+                                 int splits, float* part, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || L <= 0 || R <= 0 || page_size <= 0 || max_pages <= 0 || cache_code != out_code) return VOB_ERR_BAD_ARG;
+    if (splits < 1 || splits > 65535 || (splits > 1 && !part) || H > 65535) return VOB_ERR_BAD_ARG;
     if (L > 1024 || R > 128) return VOB_ERR_UNSUPPORTED;
     const int warps = H < 8 ? H : 8;
     const int W = L + R;
     int KT = (int)(40 * 1024 / ((size_t)W * 4));
     KT = KT > 32 ? 32 : KT < 1 ? 1 : KT;
     const size_t smem = (size_t)KT * W * 4;
-    dim3 grid(T, (H + warps - 1) / warps), block(32 * warps);
+    dim3 grid(T, (H + warps - 1) / warps, splits), block(32 * warps);
     const int nl = (L + 31) / 32;
+    int status = VOB_ERR_BAD_ARG;
 #define VOB_LA(N, TC)                                                                                                          \
-    return vob_launch(latent_attend_kernel<N, TC, TC>, grid, block, smem, stream, q_lat, q_ts, q_hs, q_rot, (const TC*)lat,   \
-                      (const TC*)kr, block_tables, max_pages, row_seq, positions, page_size, H, L, R, scale, KT, (TC*)out, o_ts, o_hs)
-#define VOB_LA_N(TC)               \
-    do {                           \
-        if (nl <= 4) VOB_LA(4, TC);    \
-        if (nl <= 8) VOB_LA(8, TC);    \
-        if (nl <= 16) VOB_LA(16, TC);  \
-        VOB_LA(32, TC);                \
+    status = vob_launch(latent_attend_kernel<N, TC, TC>, grid, block, smem, stream, q_lat, q_ts, q_hs, q_rot, (const TC*)lat, \
+                        (const TC*)kr, block_tables, max_pages, row_seq, positions, page_size, H, L, R, scale, KT, (TC*)out, o_ts, o_hs, \
+                        splits, part)
+#define VOB_LA_N(TC)                       \
+    do {                                   \
+        if (nl <= 4) { VOB_LA(4, TC); }        \
+        else if (nl <= 8) { VOB_LA(8, TC); }   \
+        else if (nl <= 16) { VOB_LA(16, TC); } \
+        else { VOB_LA(32, TC); }               \
+        if (status == 0 && splits > 1)         \
+            status = vob_launch(latent_merge_kernel<TC>, dim3(T, H), dim3(32), 0, stream, (const float*)part, positions, H, L, splits, \
+                                (TC*)out, o_ts, o_hs);                                                                          \
     } while (0)
     if (cache_code == VOB_F32) VOB_LA_N(float);
-    if (cache_code == VOB_BF16) VOB_LA_N(__nv_bfloat16);
+    else if (cache_code == VOB_BF16) VOB_LA_N(__nv_bfloat16);
 #undef VOB_LA_N
 #undef VOB_LA
-    return VOB_ERR_BAD_ARG;
+    return status;
 }

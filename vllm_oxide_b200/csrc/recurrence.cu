@@ -220,10 +220,10 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
 
 // How the key channels are shared out: KS lanes per column (a power of two), KPT registers per lane.
 static inline void scan_split(int K, int* KS, int* KPT) {
-    int ks = K <= 128 ? 4 : K <= 256 ? 8 : K <= 512 ? 16 : 32;
+    int ks = K <= 64 ? 4 : K <= 128 ? 8 : K <= 256 ? 16 : 32;
     int per = (K + ks - 1) / ks;
     *KS = ks;
-    *KPT = per <= 8 ? 8 : per <= 16 ? 16 : 32;
+    *KPT = per <= 8 ? 8 : 16;           // K <= 512: at most 16 state registers per lane
 }
 
 template <int MODE, typename TRK, typename TV>
@@ -243,8 +243,7 @@ static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const
     return vob_launch(recurrence_scan_kernel<MODE, P, TRK, TV>, grid, block, smem, stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, \
                       (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, H, K, V, KS, VT, CT)
     if (KPT == 8) VOB_SCAN(8);
-    if (KPT == 16) VOB_SCAN(16);
-    VOB_SCAN(32);
+    VOB_SCAN(16);
 #undef VOB_SCAN
 }
 
@@ -253,7 +252,7 @@ VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const voi
                                    const int* state_slots, float* o, int seqs, int H, int K, int V, cudaStream_t stream) {
     if (seqs <= 0) return 0;
     if (H <= 0 || K <= 0 || V <= 0 || H > 65535 || seqs > 65535) return VOB_ERR_BAD_ARG;
-    if (K > 1024) return VOB_ERR_UNSUPPORTED;
+    if (K > 512) return VOB_ERR_UNSUPPORTED;
     if (mode == 0 && (!w || !b || !u)) return VOB_ERR_BAD_ARG;
     if (mode == 1 && !w) return VOB_ERR_BAD_ARG;
 #define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, stream

@@ -874,10 +874,13 @@ def latent_prep(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int, 
 
 @_timed
 def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, kr: torch.Tensor, block_tables: torch.Tensor,
-                  row_seq: torch.Tensor, positions: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+                  row_seq: torch.Tensor, positions: torch.Tensor, scale: float, out: torch.Tensor, splits: int = 1,
+                  partials: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every row over its request's latent pages: score = (q_lat . c + q_rot . kr) *
     scale, softmax in float32, out_lat = sum of weights * c. q_lat float32 and out (cache type) are
-    indexed [T, heads, rank] through their strides (last stride 1); q_rot float32 [T, heads, rot]."""
+    indexed [T, heads, rank] through their strides (last stride 1); q_rot float32 [T, heads, rot].
+    `splits` > 1 shares every row's keys over that many blocks; `partials` (float32, at least
+    T * heads * splits * (rank + 2) elements) is their scratch, and a second launch merges them."""
     op = "latent_attend"
     _cuda(op, q_lat, q_rot, lat, kr, block_tables, row_seq, positions, out)
     if q_lat.dim() != 3 or q_lat.dtype != torch.float32 or q_lat.stride(2) != 1:
@@ -895,10 +898,15 @@ def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, k
         raise ShapeError(op, "block_tables must be contiguous int32 [requests, max_pages]")
     _int32_vec(row_seq, T, op, "row_seq")
     _int32_vec(positions, T, op, "positions")
-    f = _fn("latent_attention", "vob_latent_attend", [_P, _L, _L, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _L, _L, _P])
+    splits = int(splits)
+    if splits > 1:
+        _cuda(op, partials)
+        if partials is None or partials.dtype != torch.float32 or not partials.is_contiguous() or partials.numel() < T * H * splits * (L + 2):
+            raise ShapeError(op, f"{splits} splits need contiguous float32 partials of {T * H * splits * (L + 2)} elements")
+    f = _fn("latent_attention", "vob_latent_attend", [_P, _L, _L, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _L, _L, _I, _P, _P])
     _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _code(lat, op), _ptr(block_tables),
              block_tables.shape[1], _ptr(row_seq), _ptr(positions), lat.shape[2], T, H, L, R, float(scale), _ptr(out), _code(out, op),
-             out.stride(0), out.stride(1), _stream()), op)
+             out.stride(0), out.stride(1), splits, _ptr(partials) if splits > 1 else _P(0), _stream()), op, 2 if splits > 1 else 1)
 
 
 # ------------------------------------------------------------------------------------ attention

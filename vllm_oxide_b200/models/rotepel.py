@@ -70,7 +70,7 @@ def rotepel_manifest(cfg: RotepelConfig) -> Dict[str, TensorSpec]:
             for hc in subs:
                 m[p + hc + ".in"] = TensorSpec((cfg.streams,), init="ones")
                 m[p + hc + ".out"] = TensorSpec((cfg.streams,), init="ones")
-                m[p + hc + ".mix"] = TensorSpec((cfg.streams, cfg.streams))
+                m[p + hc + ".mix"] = TensorSpec((cfg.streams, cfg.streams), init="identity")
     m["final.norm"] = TensorSpec((w,), init="ones")
     m["head"] = TensorSpec((cfg.vocab, w))
     return m

@@ -45,6 +45,16 @@ class LatentAttention(Mixer):
         self.inv_freq = torch.from_numpy(rotary_inv_freq(R, rot_base).copy()).to(device)
         self.scale, self.eps, self.hidden, self.dtype = float(scale), float(eps), hidden, dtype
         self.batched = True       # bfloat16: the per-head products as one batched library product (False: one by one, tests)
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.splits = None        # a number forces so many blocks per row's keys (tests)
+
+    def key_splits(self, rows: int) -> int:
+        """Blocks that share a row's keys: steps of few rows would leave most of the GPU idle with one
+        block per row and eight heads, so their keys are shared out until the grid is about twice the SMs."""
+        if self.splits is not None:
+            return int(self.splits)
+        blocks = rows * -(-self.H // 8)
+        return max(1, min(32, 2 * self.num_sms // blocks)) if blocks < self.num_sms else 1
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return CacheSpec(kind="full", tensors=(PagedTensorSpec(1, self.L), PagedTensorSpec(1, self.R)))
@@ -54,8 +64,12 @@ class LatentAttention(Mixer):
 
     def workspace_bytes(self, rows: int) -> int:
         es, H = self.w_in.element_size(), self.H
+        parts = aligned(rows * H * self.key_splits(rows) * (self.L + 2) * 4) if self.key_splits(rows) > 1 else 0
+        if self.splits is None:     # the most any step of at most `rows` rows takes: below one block per SM every row has 32 shares
+            few = min(rows, self.num_sms // -(-H // 8))
+            parts = max(parts, aligned(few * H * 32 * (self.L + 2) * 4))
         return (aligned(rows * self.w_in.shape[0] * es) + aligned(rows * H * self.R * 4) + aligned(rows * H * self.L * 4)
-                + aligned(rows * H * self.L * es) + 2 * aligned(rows * H * self.V * es))
+                + aligned(rows * H * self.L * es) + 2 * aligned(rows * H * self.V * es) + parts)
 
     def kernel_modules(self, dtype, max_rows):
         return ("gemm_f32", "latent_attention") if dtype == torch.float32 else ("gemm_sm100", "latent_attention")
@@ -72,12 +86,15 @@ class LatentAttention(Mixer):
                             ctx.slot_mapping[cache.group] if cache.write else None, self.inv_freq, lat, kr, q_rot)
         q_heads = proj[:, :H * (D + R)].view(T, H, D + R)[:, :, :D]                 # [T, H, D], strided
         bt = ctx.block_tables[cache.group]
+        splits = self.key_splits(T)
+        partials = ctx.alloc((T * H * splits * (L + 2),), torch.float32) if splits > 1 else None
         if self.dtype == torch.bfloat16 and self.batched:
             # head-major buffers, so that each of the two per-head products is one batched product
             q_lat = ctx.alloc((H, T, L), torch.float32)
             torch.bmm(q_heads.transpose(0, 1), self.w_qlat.transpose(1, 2), out_dtype=torch.float32, out=q_lat)
             out_lat = ctx.alloc((H, T, L))
-            kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat.transpose(0, 1))
+            kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat.transpose(0, 1),
+                                  splits, partials)
             vals = ctx.alloc((H, T, V))
             torch.bmm(out_lat, self.w_val.transpose(1, 2), out=vals)
             attn = ctx.alloc((T, H * V))
@@ -87,7 +104,7 @@ class LatentAttention(Mixer):
             for h in range(H):
                 kernels.linear(q_heads[:, h], self.w_qlat[h], q_lat[:, h])
             out_lat = ctx.alloc((T, H, L))
-            kernels.latent_attend(q_lat, q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat)
+            kernels.latent_attend(q_lat, q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat, splits, partials)
             attn = ctx.alloc((T, H * V))
             for h in range(H):
                 kernels.linear(out_lat[:, h], self.w_val[h], attn[:, h * V:(h + 1) * V])

@@ -32,7 +32,7 @@ class TensorSpec:
     whatever the stored tensor has there is taken (such a tensor cannot be drawn at random)."""
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" or "int"
-    init: str = "normal"         # random-weights rule: "normal", "ones" or "zeros"
+    init: str = "normal"         # random-weights rule: "normal", "ones", "zeros" or "identity"
 
 
 class WeightSet:

@@ -2,7 +2,7 @@
 
 The reference has random weights for its tests only (crates/engine/src/testutil.rs:34-91).
 Here they are a mode of the product: each tensor of the architecture's manifest is drawn
-from N(0, std) (norm weights are ones) by a generator seeded from (seed, tensor name), so a
+from N(0, std) (norm weights are ones, mixing matrices the identity) by a generator seeded from (seed, tensor name), so a
 tensor's values do not depend on which other tensors exist or in which order they are made.
 `write_random_model` writes config.json and model.safetensors.
 """
@@ -39,6 +39,12 @@ def random_tensors(manifest: Mapping[str, TensorSpec], seed: int, std: float = 0
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            if norm_jitter:
+                t += (torch.rand(spec.shape, generator=g, device=device) * 2 - 1) * norm_jitter
+            out[name] = t.to(dtype)
+        elif spec.init == "identity":
+            # a square matrix that starts as the identity (a mixing matrix that leaves things as they are)
+            t = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device)
             if norm_jitter:
                 t += (torch.rand(spec.shape, generator=g, device=device) * 2 - 1) * norm_jitter
             out[name] = t.to(dtype)
