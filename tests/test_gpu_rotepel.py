@@ -70,7 +70,11 @@ def _tokens(n, vocab, seed):
     return [rng.randrange(vocab) for _ in range(n)]
 
 
-TOL = {"float32": 3e-5, "bfloat16": 4e-2}
+# float32: the engine against float64, rounding over a few hundred operations per logit. bfloat16: every projection's
+# input and output, the cache and the gated outputs are rounded to 8 mantissa bits (2^-9 relative each), some fifteen
+# roundings a layer run over up to seven layer runs: 2^-9 * sqrt(100) ~ 2e-2 of the largest logit as a typical row,
+# three times that for the worst logit of all rows.
+TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 
 
 def _poison(runner):

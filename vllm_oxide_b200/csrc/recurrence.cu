@@ -29,52 +29,74 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf
 //   a = sigmoid(a_in + a_bias)                          (removal rate)       b = a * u
 //   w = exp(-exp(-1/2) * sigmoid(w0 + sum_j w2[ch, j] * tanh(low[j])))       (decay, in (0.545, 1))
 // k, a_in and low (the rank-R projection) are columns of one projection output `proj` [T, ld].
-// Launch: one block of 128 threads per (token, head). All arithmetic float32.
+// Launch: one block of 128 threads per (8 tokens, head). All arithmetic float32.
 // ---------------------------------------------------------------------------------------------
+#define VOB_PREP_TOKENS 8
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
-delta_prep_kernel(const T* __restrict__ proj, long ld, int k_off, int a_off, int low_off, int R, const TW* __restrict__ w2,
-                  const float* __restrict__ w0, const float* __restrict__ a_bias, int H, int K, float* __restrict__ w_out,
+delta_prep_kernel(const T* __restrict__ proj, long ld, int k_off, int a_off, int low_off, int R, const TW* __restrict__ w2t,
+                  const float* __restrict__ w0, const float* __restrict__ a_bias, int T_rows, int H, int K, float* __restrict__ w_out,
                   float* __restrict__ b_out, float* __restrict__ u_out) {
     pdl_launch_dependents();
     pdl_wait(41);
-    extern __shared__ float th[];          // tanh of the low-rank projection, R floats
-    __shared__ float red[4];
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const T* row = proj + (size_t)t * ld;
-    for (int j = tid; j < R; j += blockDim.x) th[j] = tanhf(ld_f(row + low_off + j));
-    float ss = 0.f;
-    for (int c = tid; c < K; c += blockDim.x) {
-        const float kv = ld_f(row + k_off + h * K + c);
-        ss = fmaf(kv, kv, ss);
+    extern __shared__ float th[];          // tanh of the low-rank projection, [VOB_PREP_TOKENS][R]
+    __shared__ float red[VOB_PREP_TOKENS][4];
+    const int t0 = blockIdx.x * VOB_PREP_TOKENS, h = blockIdx.y, tid = threadIdx.x;
+    const int nt = min(VOB_PREP_TOKENS, T_rows - t0);
+    for (int e = tid; e < nt * R; e += blockDim.x) {
+        const int tt = e / R, j = e - tt * R;
+        th[e] = tanhf(ld_f(proj + (size_t)(t0 + tt) * ld + low_off + j));
     }
-    ss = warp_sum(ss);
-    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    for (int tt = 0; tt < nt; ++tt) {
+        const T* row = proj + (size_t)(t0 + tt) * ld;
+        float ss = 0.f;
+        for (int c = tid; c < K; c += blockDim.x) {
+            const float kv = ld_f(row + k_off + h * K + c);
+            ss = fmaf(kv, kv, ss);
+        }
+        ss = warp_sum(ss);
+        if ((tid & 31) == 0) red[tt][tid >> 5] = ss;
+    }
     __syncthreads();
-    const float inv = 1.0f / sqrtf((red[0] + red[1]) + (red[2] + red[3]) + 1e-6f);
+    const int HK = H * K;
     for (int c = tid; c < K; c += blockDim.x) {
         const int ch = h * K + c;
-        const float kv = ld_f(row + k_off + ch);
-        const float u = kv * inv;
-        const float a = sigmoidf_(ld_f(row + a_off + ch) + a_bias[ch]);
-        float low = w0[ch];
-        const TW* wr = w2 + (size_t)ch * R;
-        for (int j = 0; j < R; ++j) low = fmaf(ld_f(wr + j), th[j], low);
-        const size_t o = (size_t)t * H * K + ch;
-        w_out[o] = expf(-0.6065306597126334f * sigmoidf_(low));
-        b_out[o] = a * u;
-        u_out[o] = u;
+        float low[VOB_PREP_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < VOB_PREP_TOKENS; ++tt) low[tt] = w0[ch];
+        // w2t is [R, H * K]: neighbouring threads read neighbouring channels; every element serves all the block's tokens
+        for (int j = 0; j < R; ++j) {
+            const float wv = ld_f(w2t + (size_t)j * HK + ch);
+#pragma unroll
+            for (int tt = 0; tt < VOB_PREP_TOKENS; ++tt) low[tt] = fmaf(wv, th[tt * R + j], low[tt]);
+        }
+        const float ab = a_bias[ch];
+#pragma unroll
+        for (int tt = 0; tt < VOB_PREP_TOKENS; ++tt) {
+            if (tt < nt) {
+                const T* row = proj + (size_t)(t0 + tt) * ld;
+                const float inv = 1.0f / sqrtf((red[tt][0] + red[tt][1]) + (red[tt][2] + red[tt][3]) + 1e-6f);
+                const float u = ld_f(row + k_off + ch) * inv;
+                const float a = sigmoidf_(ld_f(row + a_off + ch) + ab);
+                const size_t o = (size_t)(t0 + tt) * HK + ch;
+                w_out[o] = expf(-0.6065306597126334f * sigmoidf_(low[tt]));
+                b_out[o] = a * u;
+                u_out[o] = u;
+            }
+        }
     }
 }
 
-VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, int a_off, int low_off, int R, const void* w2,
+// w2t: the second decay projection transposed, [R, H * K].
+VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, int a_off, int low_off, int R, const void* w2t,
                               int w2_code, const float* w0, const float* a_bias, int T, int H, int K, float* w_out, float* b_out,
                               float* u_out, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || K <= 0 || R <= 0 || H > 65535 || (size_t)R * 4 > 40 * 1024) return VOB_ERR_BAD_ARG;
+    if (H <= 0 || K <= 0 || R <= 0 || H > 65535 || (size_t)R * 4 * VOB_PREP_TOKENS > 40 * 1024) return VOB_ERR_BAD_ARG;
     if (code != w2_code) return VOB_ERR_BAD_ARG;
-    VOB_DISPATCH_ELEM(code, return vob_launch(delta_prep_kernel<ElemT, ElemT>, dim3(T, H), dim3(128), (size_t)R * 4, stream,
-                                              (const ElemT*)proj, ld, k_off, a_off, low_off, R, (const ElemT*)w2, w0, a_bias, H, K,
+    const int blocks = (T + VOB_PREP_TOKENS - 1) / VOB_PREP_TOKENS;
+    VOB_DISPATCH_ELEM(code, return vob_launch(delta_prep_kernel<ElemT, ElemT>, dim3(blocks, H), dim3(128), (size_t)R * 4 * VOB_PREP_TOKENS,
+                                              stream, (const ElemT*)proj, ld, k_off, a_off, low_off, R, (const ElemT*)w2t, w0, a_bias, T, H, K,
                                               w_out, b_out, u_out));
     return 0;
 }
@@ -133,8 +155,9 @@ VOB_EXPORT int vob_rotate_scale(const void* src, int code, long ld, const int* p
 // A request's rows are seq_starts[s] .. seq_starts[s + 1] - 1 (none: the block leaves at once and
 // its state slot is not touched).
 // ---------------------------------------------------------------------------------------------
+#define VOB_SCAN_PRE 24
 template <int MODE, int KPT, typename TRK, typename TV>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 1)
 recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restrict__ k, long ld_k, const TV* __restrict__ v,
                        long ld_v, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ u,
                        float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
@@ -164,28 +187,55 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
         S[i] = (col && c < K) ? S_glob[(size_t)c * V + j] : 0.f;
     }
     const float decay = MODE == 1 ? w[h] : 0.f;
+    // What one token needs, as one list of elements: r, k (and w, b, u) over KPAD channels, then v over VT columns.
+    // The list of the next CT tokens is fetched into registers (PRE per thread) while the staged tokens are worked
+    // on, so that a token's step never waits for memory: the chain from token to token is what bounds a long portion.
+    const int NA = MODE == 0 ? 5 : 2;
+    const int per_token = NA * KPAD + VT;
+    float pre[VOB_SCAN_PRE];
+    auto fetch = [&](int c0, int n) {
+#pragma unroll
+        for (int i = 0; i < VOB_SCAN_PRE; ++i) {
+            const int e = tid + i * nthr;
+            float val = 0.f;
+            if (e < n * per_token) {
+                const int tt = e / per_token, x = e - tt * per_token;
+                const size_t row = (size_t)(c0 + tt);
+                if (x < NA * KPAD) {
+                    const int a = x / KPAD, c = x - a * KPAD;
+                    if (c < K) {
+                        const size_t g = row * H * K + h * K + c;
+                        val = a == 0 ? ld_f(r + row * ld_r + h * K + c) : a == 1 ? ld_f(k + row * ld_k + h * K + c)
+                            : a == 2 ? w[g] : a == 3 ? b[g] : u[g];
+                    }
+                } else {
+                    const int jv = blockIdx.x * VT + (x - NA * KPAD);
+                    if (jv < V) val = ld_f(v + row * ld_v + h * V + jv);
+                }
+            }
+            pre[i] = val;
+        }
+    };
+    fetch(r0, min(CT, r1 - r0));
     for (int c0 = r0; c0 < r1; c0 += CT) {
         const int n = min(CT, r1 - c0);
         __syncthreads();                     // the tokens staged before have been used
-        for (int e = tid; e < n * KPAD; e += nthr) {
-            const int tt = e / KPAD, c = e - tt * KPAD;
-            const size_t row = (size_t)(c0 + tt);
-            const bool in = c < K;
-            sr[e] = in ? ld_f(r + row * ld_r + h * K + c) : 0.f;
-            sk[e] = in ? ld_f(k + row * ld_k + h * K + c) : 0.f;
-            if (MODE == 0) {
-                const size_t g = row * H * K + h * K + c;
-                sw[e] = in ? w[g] : 0.f;
-                sb[e] = in ? b[g] : 0.f;
-                su[e] = in ? u[g] : 0.f;
+#pragma unroll
+        for (int i = 0; i < VOB_SCAN_PRE; ++i) {
+            const int e = tid + i * nthr;
+            if (e < n * per_token) {
+                const int tt = e / per_token, x = e - tt * per_token;
+                if (x < NA * KPAD) {
+                    const int a = x / KPAD, c = x - a * KPAD;
+                    float* dst = a == 0 ? sr : a == 1 ? sk : a == 2 ? sw : a == 3 ? sb : su;
+                    dst[tt * KPAD + c] = pre[i];
+                } else {
+                    sv[tt * VT + (x - NA * KPAD)] = pre[i];
+                }
             }
         }
-        for (int e = tid; e < n * VT; e += nthr) {
-            const int tt = e / VT, c = e - tt * VT;
-            const int jv = blockIdx.x * VT + c;
-            sv[e] = jv < V ? ld_f(v + (size_t)(c0 + tt) * ld_v + h * V + jv) : 0.f;
-        }
         __syncthreads();
+        if (c0 + CT < r1) fetch(c0 + CT, min(CT, r1 - c0 - CT));
         for (int tt = 0; tt < n; ++tt) {
             const float* pr = sr + tt * KPAD + q;
             const float* pk = sk + tt * KPAD + q;
@@ -235,9 +285,11 @@ static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const
     const int VT = 128 / KS;
     const int KPAD = KS * KPT;
     const size_t per_token = (size_t)((MODE == 0 ? 5 : 2) * KPAD + VT) * 4;
-    int CT = (int)(40 * 1024 / per_token);
-    CT = CT > 16 ? 16 : CT < 1 ? 1 : CT;
-    const size_t smem = per_token * CT;
+    // tokens staged at a time: what the block's 128 threads can hold of the next ones in VOB_SCAN_PRE registers each
+    int CT = (int)((size_t)VOB_SCAN_PRE * 128 * 4 / per_token);
+    CT = CT > 16 ? 16 : CT;
+    if (CT < 1) return VOB_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(5 * KPAD + VT) * 4 * CT;
     dim3 grid((V + VT - 1) / VT, H, seqs), block(VT * KS);
 #define VOB_SCAN(P)                                                                                                            \
     return vob_launch(recurrence_scan_kernel<MODE, P, TRK, TV>, grid, block, smem, stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, \

@@ -740,18 +740,18 @@ def stream_norm(streams: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[
 
 # ------------------------------------------------------------------------------------ linear recurrences
 @_timed
-def delta_prep(proj: torch.Tensor, k_off: int, a_off: int, low_off: int, rank: int, w2: torch.Tensor, w0: torch.Tensor,
+def delta_prep(proj: torch.Tensor, k_off: int, a_off: int, low_off: int, rank: int, w2t: torch.Tensor, w0: torch.Tensor,
                a_bias: torch.Tensor, heads: int, dim: int, w_out: torch.Tensor, b_out: torch.Tensor, u_out: torch.Tensor) -> None:
     """What the delta-rule recurrence reads besides r, k, v, per token, head and key channel, all float32
     [T, heads * dim]: u = k / sqrt(sum k^2 + 1e-6) per head; b = sigmoid(a + a_bias) * u;
     w = exp(-exp(-1/2) * sigmoid(w0 + w2 tanh(low))). k, a and low (width `rank`) are the columns
-    k_off.., a_off.., low_off.. of `proj` [T, ld]."""
+    k_off.., a_off.., low_off.. of `proj` [T, ld]; `w2t` is w2 transposed, [rank, heads * dim]."""
     op = "delta_prep"
-    _cuda(op, proj, w2, w0, a_bias, w_out, b_out, u_out)
+    _cuda(op, proj, w2t, w0, a_bias, w_out, b_out, u_out)
     _rows_2d(proj, op, "proj")
     T, hd = proj.shape[0], heads * dim
-    if w2.shape != (hd, rank) or not w2.is_contiguous() or w2.dtype != proj.dtype:
-        raise ShapeError(op, f"w2 must be contiguous {proj.dtype} [{hd}, {rank}], got {w2.dtype} {list(w2.shape)}")
+    if w2t.shape != (rank, hd) or not w2t.is_contiguous() or w2t.dtype != proj.dtype:
+        raise ShapeError(op, f"w2t must be contiguous {proj.dtype} [{rank}, {hd}], got {w2t.dtype} {list(w2t.shape)}")
     _f32_vec(w0, hd, op, "w0")
     _f32_vec(a_bias, hd, op, "a_bias")
     for name, t in (("w_out", w_out), ("b_out", b_out), ("u_out", u_out)):
@@ -761,7 +761,7 @@ def delta_prep(proj: torch.Tensor, k_off: int, a_off: int, low_off: int, rank: i
         if off < 0 or off + n > proj.shape[1]:
             raise ShapeError(op, f"columns {off}..{off + n} lie outside proj's {proj.shape[1]}")
     f = _fn("recurrence", "vob_delta_prep", [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _P])
-    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), k_off, a_off, low_off, rank, _ptr(w2), _code(w2, op), _ptr(w0), _ptr(a_bias),
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), k_off, a_off, low_off, rank, _ptr(w2t), _code(w2t, op), _ptr(w0), _ptr(a_bias),
              T, heads, dim, _ptr(w_out), _ptr(b_out), _ptr(u_out), _stream()), op)
 
 

@@ -50,7 +50,7 @@ class GeneralDelta(Mixer):
                 raise ValueError(f"'{name}' must have {hd} entries, got {list(t.shape)}")
         # one matrix [Wr; Wk; Wv; Wa; Wg; Ww1]: a single product gives every projection of the input
         self.w_in = to_compute(torch.cat([wr, wk, wv, wa, wg, w1], dim=0), dtype, device)
-        self.w2 = to_compute(w2, dtype, device)
+        self.w2t = to_compute(w2.t(), dtype, device)          # [rank, heads * dim]: the kernel reads it channel by channel
         self.w_o = to_compute(wo, dtype, device)
         f32 = dict(device=device, dtype=torch.float32)
         self.a_bias, self.w0, self.norm_weight = a_bias.to(**f32).contiguous(), w0.to(**f32).contiguous(), norm_weight.to(**f32).contiguous()
@@ -60,7 +60,7 @@ class GeneralDelta(Mixer):
         return StateSpec((self.H, self.D, self.D), torch.float32)
 
     def weight_bytes(self) -> int:
-        return (self.w_in.numel() + self.w2.numel() + self.w_o.numel()) * self.w_in.element_size()
+        return (self.w_in.numel() + self.w2t.numel() + self.w_o.numel()) * self.w_in.element_size()
 
     def workspace_bytes(self, rows: int) -> int:
         es, hd = self.w_in.element_size(), self.H * self.D
@@ -75,7 +75,7 @@ class GeneralDelta(Mixer):
         T, hd = x.shape[0], self.H * self.D
         proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
         w, b, u, o = (ctx.alloc((T, hd), torch.float32) for _ in range(4))
-        kernels.delta_prep(proj, hd, 3 * hd, 5 * hd, self.rank, self.w2, self.w0, self.a_bias, self.H, self.D, w, b, u)
+        kernels.delta_prep(proj, hd, 3 * hd, 5 * hd, self.rank, self.w2t, self.w0, self.a_bias, self.H, self.D, w, b, u)
         kernels.recurrence_scan(0, proj[:, :hd], proj[:, hd:2 * hd], proj[:, 2 * hd:3 * hd], w, b, u, state, ctx.seq_starts,
                                 ctx.state_slots, ctx.seqs, self.H, o)
         gated = ctx.alloc((T, hd))
