@@ -707,7 +707,7 @@ def rotepel_roofline(rs, blocks, n, batch, peaks, prefill, decode):
     out = {}
 
     def add(name, phase, totals, nbytes=None, flops=None):
-        ms = sum(t for op, _, t in totals if op == name)
+        ms = sum(t for op, _, t in totals if op == name or op == name + "_tc")      # the tensor-core form of a kernel counts with it
         if ms <= 0:
             return
         e = {"ms": round(ms, 4)}

@@ -279,6 +279,54 @@ def test_latent_attend_kernel_far_key_page_borders_and_first_tokens(dtype):
     assert torch.all(out2[7] == 0) and torch.equal(out2[8:], out[8:])
 
 
+def test_latent_attend_tensor_core_kernel_against_float64():
+    """Prompt portions on the tensor cores: two requests in one launch, the second with 37 keys already cached,
+    pages scattered, five heads (a block of four and a block of one), tiles of 16 tokens that end inside a
+    portion, one dominant key far back and one at the row's own position."""
+    from vllm_oxide_b200 import kernels
+    torch.manual_seed(4)
+    H, L, R, page, scale = 5, 48, 16, 8, 0.4
+    lens, ctxs = (100, 50), (0, 37)
+    total = [c + n for c, n in zip(ctxs, lens)]
+    pages_per = [-(-t // page) for t in total]
+    perm = torch.randperm(sum(pages_per) + 4)
+    tables = torch.full((2, max(pages_per) + 2), -1, dtype=torch.int32)
+    tables[0, :pages_per[0]] = perm[:pages_per[0]].to(torch.int32)
+    tables[1, :pages_per[1]] = perm[pages_per[0]:sum(pages_per)].to(torch.int32)
+    lat_c = torch.full((sum(pages_per) + 4, 1, page, L), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kr_c = torch.full((sum(pages_per) + 4, 1, page, R), float("nan"), dtype=torch.bfloat16, device=DEV)
+    c = [torch.randn(t, L) * 0.5 for t in total]
+    kr = [torch.randn(t, R) * 0.5 for t in total]
+    T = sum(lens)
+    q_lat, q_rot = torch.randn(T, H, L) * 0.3, torch.randn(T, H, R) * 0.3
+    q_lat[99] = 8.0 * c[0][3] / c[0][3].norm() ** 2 / scale            # row 99 of request 0 looks for key 3
+    q_lat[100 + 20] = 8.0 * c[1][57] / c[1][57].norm() ** 2 / scale    # row 20 of request 1 (position 57) looks for its own key
+    for s in range(2):
+        idx = torch.arange(total[s])
+        slot = tables[s, idx // page].long() * page + idx % page
+        lat_c.view(-1, L)[slot.to(DEV)] = c[s].to(device=DEV, dtype=torch.bfloat16)
+        kr_c.view(-1, R)[slot.to(DEV)] = kr[s].to(device=DEV, dtype=torch.bfloat16)
+    positions = torch.cat([torch.arange(ctxs[s], total[s]) for s in range(2)]).to(device=DEV, dtype=torch.int32)
+    starts = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, H, L, dtype=torch.bfloat16, device=DEV)
+    assert kernels.latent_attend_tc_supported(H, L, R) and not kernels.latent_attend_tc_supported(H, 40, 8)
+    kernels.latent_attend_tc(q_lat.to(DEV), q_rot.to(DEV), lat_c, kr_c, tables.to(DEV), starts, positions, 2, 100, scale, out)
+    r0 = 0
+    for s in range(2):
+        cc, kk = c[s].bfloat16().double(), kr[s].bfloat16().double()
+        ql, qr = q_lat[r0:r0 + lens[s]].bfloat16().double(), q_rot[r0:r0 + lens[s]].bfloat16().double()
+        score = (torch.einsum("ihl,jl->hij", ql, cc) + torch.einsum("ihr,jr->hij", qr, kk)) * scale
+        visible = torch.arange(total[s])[None, :] <= torch.arange(ctxs[s], total[s])[:, None]
+        p = torch.softmax(score.masked_fill(~visible, float("-inf")), -1)
+        want = torch.einsum("hij,jl->ihl", p, cc)
+        assert max_rel_diff(out[r0:r0 + lens[s]].cpu(), want) < 1.5e-2, s
+        if s == 0:
+            assert float(p[:, 99, 3].min()) > 0.5            # the far key is what row 99 is made of
+        else:
+            assert float(p[:, 20, 57].min()) > 0.5
+        r0 += lens[s]
+
+
 # ------------------------------------------------------------------------------------ models in the engine
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["delta", "retention", "latent"])

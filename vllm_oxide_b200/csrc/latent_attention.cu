@@ -17,6 +17,7 @@
 // puts together in a fixed order.
 #include "common.cuh"
 #include <math.h>
+#include <mma.h>
 VOB_PDL_SWITCH(latent_attention)
 
 // proj [T, ld]: the query of head h at columns q_off + h * (D + R) (D plain features, then R to be
@@ -132,35 +133,59 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
     for (int k0 = blockIdx.z * share; k0 < nkeys; k0 += KT) {
         const int n = min(KT, nkeys - k0);
         __syncthreads();
-        for (int e = threadIdx.x; e < n * W; e += blockDim.x) {
-            const int kk = e / W, c = e - kk * W;
+        // a warp copies whole keys (one page lookup per key, then consecutive elements)
+        for (int kk = warp; kk < n; kk += (int)(blockDim.x >> 5)) {
             const int key = k0 + kk;
             const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
-            tile[e] = c < L ? ld_f(lat + slot * L + c) : ld_f(kr + slot * R + (c - L));
+            float* dst = tile + kk * W;
+            for (int c = lane; c < L; c += 32) dst[c] = ld_f(lat + slot * L + c);
+            for (int c = lane; c < R; c += 32) dst[L + c] = ld_f(kr + slot * R + c);
         }
         __syncthreads();
-        for (int kk = 0; kk < n; ++kk) {
-            const float* kv = tile + kk * W;
-            float sc = 0.f;
+        // four keys at a time: their dot products and reductions are independent chains
+        for (int kk = 0; kk < n; kk += 4) {
+            float sc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float* kv = tile + min(kk + j, n - 1) * W;
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < NL; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < L) a = fmaf(ql[i], kv[c], a);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < R) a = fmaf(qr[i], kv[L + c], a);
+                }
+                sc[j] = a;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[j] += __shfl_xor_sync(0xffffffffu, sc[j], o);
+            }
+            float mn = m;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                sc[j] = kk + j < n ? sc[j] * scale : -INFINITY;
+                mn = fmaxf(mn, sc[j]);
+            }
+            const float corr = expf(m - mn);            // exp(-inf) = 0 at the first keys
+            float p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) p[j] = expf(sc[j] - mn);
+            l = fmaf(l, corr, (p[0] + p[1]) + (p[2] + p[3]));
 #pragma unroll
             for (int i = 0; i < NL; ++i) {
                 const int c = lane + 32 * i;
-                if (c < L) sc = fmaf(ql[i], kv[c], sc);
-            }
+                float a = acc[i] * corr;
+                if (c < L) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int c = lane + 32 * i;
-                if (c < R) sc = fmaf(qr[i], kv[L + c], sc);
-            }
-            sc = warp_sum(sc) * scale;
-            const float mn = fmaxf(m, sc);
-            const float corr = expf(m - mn);            // exp(-inf) = 0 at the first key
-            const float p = expf(sc - mn);
-            l = fmaf(l, corr, p);
-#pragma unroll
-            for (int i = 0; i < NL; ++i) {
-                const int c = lane + 32 * i;
-                acc[i] = fmaf(p, c < L ? kv[c] : 0.f, acc[i] * corr);
+                    for (int j = 0; j < 4; ++j) a = fmaf(p[j], tile[min(kk + j, n - 1) * W + c], a);
+                }
+                acc[i] = a;
             }
             m = mn;
         }
@@ -248,4 +273,166 @@ VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const
 #undef VOB_LA_N
 #undef VOB_LA
     return status;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Prompt portions in bfloat16 on the tensor cores (mma.sync through the wmma interface). A block takes 16
+// consecutive tokens of one request and up to 4 heads, one warp per head; a tile of 32 keys ([c | kr], L + R
+// wide) is brought into shared memory once for all of them. Per warp and key tile: S = Q K^T (float32
+// accumulation), the softmax of its 16 rows in float32 with the running maximum and sum in registers, P in
+// bfloat16, O += P C with O in shared memory as float32 (rescaled row by row when a maximum moves).
+// Needs L and R multiples of 16. Rows are a request's seq_starts[s] + 16 * tile .. ; their positions are
+// consecutive, so the tile's last row bounds the keys and every row masks what lies behind its own position.
+// ---------------------------------------------------------------------------------------------
+#define VOB_LTC_BN 32
+__global__ void __launch_bounds__(128, 1)
+latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
+                        const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ kr, const int* __restrict__ block_tables,
+                        int max_pages, const int* __restrict__ seq_starts, const int* __restrict__ positions, int page_size, int H, int L,
+                        int R, float scale, __nv_bfloat16* __restrict__ out, long o_ts, long o_hs) {
+    using namespace nvcuda;
+    constexpr int BN = VOB_LTC_BN;
+    pdl_launch_dependents();
+    pdl_wait(48);
+    const int s = blockIdx.z, HB = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * HB + warp;
+    const bool head = h < H;
+    const int r0 = seq_starts[s] + blockIdx.x * 16, r1 = seq_starts[s + 1];
+    if (r0 >= r1) return;
+    const int nrows = min(16, r1 - r0);
+    const int D = L + R;
+    // leading dimensions with a few elements of padding: rows 512 or 1,024 bytes apart would all fall into the same banks
+    const int DP = D + 8, LO = L + 4;
+    constexpr int LS = BN + 4, LP = BN + 8;
+    extern __shared__ __align__(128) unsigned char ltc_smem[];
+    __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(ltc_smem);                               // [BN][DP]
+    __nv_bfloat16* Q = Kt + (size_t)BN * DP + (size_t)warp * 16 * DP;                              // [16][DP] per warp
+    float* obase = reinterpret_cast<float*>(Kt + (size_t)BN * DP + (size_t)HB * 16 * DP);
+    float* O = obase + (size_t)warp * 16 * LO;                                                     // [16][LO] per warp
+    float* S = obase + (size_t)HB * 16 * LO + warp * 16 * LS;                                      // [16][LS] per warp
+    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(obase + (size_t)HB * 16 * LO + HB * 16 * LS) + warp * 16 * LP;
+    for (int e = lane; e < 16 * D; e += 32) {
+        const int i = e / D, c = e - i * D;
+        float v = 0.f;
+        if (head && i < nrows)
+            v = c < L ? q_lat[(size_t)(r0 + i) * q_ts + (size_t)h * q_hs + c] : q_rot[((size_t)(r0 + i) * H + h) * R + (c - L)];
+        Q[i * DP + c] = __float2bfloat16_rn(v);
+    }
+    for (int e = lane; e < 16 * LO; e += 32) O[e] = 0.f;
+    const int pos0 = positions[r0], pos_hi = pos0 + nrows - 1;
+    const int* table = block_tables + (size_t)s * max_pages;
+    float m[16], l[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
+    const int lat_chunks = L / 8, kr_chunks = R / 8;            // 16-byte pieces of a key
+    for (int k0 = 0; k0 <= pos_hi; k0 += BN) {
+        __syncthreads();
+        for (int kk = warp; kk < BN; kk += HB) {
+            const int key = k0 + kk;
+            uint4* dst = reinterpret_cast<uint4*>(Kt + (size_t)kk * DP);
+            if (key <= pos_hi) {
+                const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
+                const uint4* a = reinterpret_cast<const uint4*>(lat + slot * L);
+                const uint4* b = reinterpret_cast<const uint4*>(kr + slot * R);
+                for (int c = lane; c < lat_chunks; c += 32) dst[c] = a[c];
+                for (int c = lane; c < kr_chunks; c += 32) dst[lat_chunks + c] = b[c];
+            } else {
+                for (int c = lane; c < lat_chunks + kr_chunks; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        __syncthreads();
+        if (!head) continue;
+        // S = Q K^T
+#pragma unroll
+        for (int nt = 0; nt < BN / 16; ++nt) {
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
+            wmma::fill_fragment(c, 0.f);
+            for (int ks = 0; ks < D / 16; ++ks) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
+                wmma::load_matrix_sync(a, Q + ks * 16, DP);
+                wmma::load_matrix_sync(b, Kt + (size_t)nt * 16 * DP + ks * 16, DP);
+                wmma::mma_sync(c, a, b, c);
+            }
+            wmma::store_matrix_sync(S + nt * 16, c, LS, wmma::mem_row_major);
+        }
+        __syncwarp();
+        // the softmax of the warp's 16 rows, one key per lane
+        const int key = k0 + lane;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float sc = S[i * LS + lane] * scale;
+            if (i >= nrows || key > pos0 + i) sc = -INFINITY;
+            const float mn = fmaxf(m[i], warp_max(sc));
+            const bool none = mn == -INFINITY;
+            const float p = none ? 0.f : expf(sc - mn);
+            const float corr = none ? 1.f : expf(m[i] - mn);
+            l[i] = fmaf(l[i], corr, warp_sum(p));
+            m[i] = mn;
+            P[i * LP + lane] = __float2bfloat16_rn(p);
+            if (corr != 1.f)
+                for (int c = lane; c < L; c += 32) O[i * LO + c] *= corr;
+        }
+        __syncwarp();
+        // O += P C
+        for (int nt = 0; nt < L / 16; ++nt) {
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
+            wmma::load_matrix_sync(c, O + nt * 16, LO, wmma::mem_row_major);
+#pragma unroll
+            for (int ks = 0; ks < BN / 16; ++ks) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::row_major> b;
+                wmma::load_matrix_sync(a, P + ks * 16, LP);
+                wmma::load_matrix_sync(b, Kt + (size_t)ks * 16 * DP + nt * 16, DP);
+                wmma::mma_sync(c, a, b, c);
+            }
+            wmma::store_matrix_sync(O + nt * 16, c, LO, wmma::mem_row_major);
+        }
+        __syncwarp();
+    }
+    if (!head) return;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (i < nrows) {
+            const float inv = 1.0f / l[i];
+            __nv_bfloat16* orow = out + (size_t)(r0 + i) * o_ts + (size_t)h * o_hs;
+            for (int c = lane; c < L; c += 32) orow[c] = __float2bfloat16_rn(O[i * LO + c] * inv);
+        }
+    }
+}
+
+// Heads a block of the tensor-core kernel takes (0: the sizes do not fit it).
+static int ltc_heads(int H, int L, int R) {
+    if (L % 16 || R % 16 || L <= 0 || R <= 0) return 0;
+    const size_t DP = (size_t)L + R + 8;
+    const size_t shared = (size_t)VOB_LTC_BN * DP * 2;
+    const size_t per_head = 16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2;
+    if (shared + per_head > 200 * 1024) return 0;
+    int hb = (int)((200 * 1024 - shared) / per_head);
+    hb = hb > 4 ? 4 : hb;
+    return hb > H ? H : hb;
+}
+
+VOB_EXPORT int vob_latent_attend_tc_supported(int H, int L, int R) { return ltc_heads(H, L, R) > 0 ? 1 : 0; }
+
+// q_lat, q_rot, out and the caches as for vob_latent_attend (bfloat16 caches and out only); seq_starts int32
+// [seqs + 1]; max_new: no request brings more rows than this.
+VOB_EXPORT int vob_latent_attend_tc(const float* q_lat, long q_ts, long q_hs, const float* q_rot, const void* lat, const void* kr,
+                                    const int* block_tables, int max_pages, const int* seq_starts, const int* positions, int page_size,
+                                    int seqs, int max_new, int H, int L, int R, float scale, void* out, long o_ts, long o_hs,
+                                    cudaStream_t stream) {
+    if (seqs <= 0 || max_new <= 0) return 0;
+    const int hb = ltc_heads(H, L, R);
+    if (hb <= 0) return VOB_ERR_UNSUPPORTED;
+    if (page_size <= 0 || max_pages <= 0 || seqs > 65535 || (H + hb - 1) / hb > 65535) return VOB_ERR_BAD_ARG;
+    const size_t DP = (size_t)L + R + 8;
+    const size_t smem = (size_t)VOB_LTC_BN * DP * 2
+        + (size_t)hb * (16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2);
+    cudaError_t e = cudaFuncSetAttribute(latent_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return vob_launch(latent_attend_tc_kernel, dim3((max_new + 15) / 16, (H + hb - 1) / hb, seqs), dim3(32 * hb), smem, stream, q_lat, q_ts,
+                      q_hs, q_rot, (const __nv_bfloat16*)lat, (const __nv_bfloat16*)kr, block_tables, max_pages, seq_starts, positions,
+                      page_size, H, L, R, scale, (__nv_bfloat16*)out, o_ts, o_hs);
 }

@@ -11,7 +11,7 @@
 // columns of one head of one request, KS threads share a column (thread q of them holds key
 // channels q, q + KS, ... in registers) and the two dot products over key channels are finished
 // by shuffles among those KS lanes, in a fixed order. The block walks the request's rows of this
-// step in order, CT tokens at a time staged in shared memory. A step of one token is the same
+// step in order, a few tokens at a time staged in shared memory. A step of one token is the same
 // kernel: read the state, one update, write it back (bound by the state's bytes). The arithmetic
 // of a token never depends on how the tokens were cut into steps or what else is in the batch.
 //
@@ -153,29 +153,28 @@ VOB_EXPORT int vob_rotate_scale(const void* src, int code, long ld, const int* p
 // r, k: [T, >= H * K] with row strides; v: [T, >= H * V]; w, b, u: float32 [T, H * K] (mode 0) or
 // w = float32 [H] (mode 1); state float32 [slots, H, K, V]; o float32 [T, H * V].
 // A request's rows are seq_starts[s] .. seq_starts[s + 1] - 1 (none: the block leaves at once and
-// its state slot is not touched).
+// its state slot is not touched). VT = 128 / KS.
 // ---------------------------------------------------------------------------------------------
-#define VOB_SCAN_PRE 24
-template <int MODE, int KPT, typename TRK, typename TV>
+template <int MODE, int KPT, int KS, typename TRK, typename TV>
 __global__ void __launch_bounds__(128, 1)
 recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restrict__ k, long ld_k, const TV* __restrict__ v,
                        long ld_v, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ u,
                        float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
-                       float* __restrict__ o, int H, int K, int V, int KS, int VT, int CT) {
+                       float* __restrict__ o, int H, int K, int V) {
+    // Every size of the tiling is a constant, so that staging a token is a few plain loads and stores: what one token
+    // needs is one list of PER elements (r, k and in mode 0 w, b, u over KPAD channels, then v over VT columns), thread
+    // t takes elements t, t + 128, ... of it (NPT per token), and the list of the next CT tokens is fetched into
+    // registers while the staged tokens are worked on. The chain from token to token is what bounds a long portion.
+    constexpr int KPAD = KS * KPT, VT = 128 / KS, NA = MODE == 0 ? 5 : 2;
+    constexpr int PER = NA * KPAD + VT, NPT = (PER + 127) / 128;
+    constexpr int CT = NPT >= 24 ? 1 : (24 / NPT > 8 ? 8 : 24 / NPT);
     pdl_launch_dependents();
     pdl_wait(43);
     const int s = blockIdx.z, h = blockIdx.y;
     const int r0 = seq_starts[s], r1 = seq_starts[s + 1];
     if (r1 <= r0) return;
-    extern __shared__ float sm[];
-    const int KPAD = KS * KPT;
-    float* sr = sm;                          // [CT][KPAD]
-    float* sk = sr + CT * KPAD;
-    float* sv = sk + CT * KPAD;              // [CT][VT]
-    float* sw = sv + CT * VT;                // mode 0 only: [CT][KPAD] each
-    float* sb = sw + CT * KPAD;
-    float* su = sb + CT * KPAD;
-    const int tid = threadIdx.x, nthr = blockDim.x;
+    __shared__ float sm[CT * PER];           // token tt: [r | k | (w | b | u) | v] at sm + tt * PER
+    const int tid = threadIdx.x;
     const int q = tid % KS, jj = tid / KS;
     const int j = blockIdx.x * VT + jj;
     const bool col = j < V;
@@ -187,33 +186,30 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
         S[i] = (col && c < K) ? S_glob[(size_t)c * V + j] : 0.f;
     }
     const float decay = MODE == 1 ? w[h] : 0.f;
-    // What one token needs, as one list of elements: r, k (and w, b, u) over KPAD channels, then v over VT columns.
-    // The list of the next CT tokens is fetched into registers (PRE per thread) while the staged tokens are worked
-    // on, so that a token's step never waits for memory: the chain from token to token is what bounds a long portion.
-    const int NA = MODE == 0 ? 5 : 2;
-    const int per_token = NA * KPAD + VT;
-    float pre[VOB_SCAN_PRE];
+    float pre[CT * NPT];
     auto fetch = [&](int c0, int n) {
 #pragma unroll
-        for (int i = 0; i < VOB_SCAN_PRE; ++i) {
-            const int e = tid + i * nthr;
-            float val = 0.f;
-            if (e < n * per_token) {
-                const int tt = e / per_token, x = e - tt * per_token;
-                const size_t row = (size_t)(c0 + tt);
-                if (x < NA * KPAD) {
-                    const int a = x / KPAD, c = x - a * KPAD;
-                    if (c < K) {
-                        const size_t g = row * H * K + h * K + c;
-                        val = a == 0 ? ld_f(r + row * ld_r + h * K + c) : a == 1 ? ld_f(k + row * ld_k + h * K + c)
-                            : a == 2 ? w[g] : a == 3 ? b[g] : u[g];
+        for (int tt = 0; tt < CT; ++tt) {
+            const size_t row = (size_t)(c0 + tt);
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int x = tid + i * 128;            // which array and channel x is does not depend on the token
+                float val = 0.f;
+                if (tt < n && x < PER) {
+                    if (x < NA * KPAD) {
+                        const int a = x / KPAD, c = x % KPAD;
+                        if (c < K) {
+                            const size_t g = row * H * K + h * K + c;
+                            val = a == 0 ? ld_f(r + row * ld_r + h * K + c) : a == 1 ? ld_f(k + row * ld_k + h * K + c)
+                                : a == 2 ? w[g] : a == 3 ? b[g] : u[g];
+                        }
+                    } else {
+                        const int jv = blockIdx.x * VT + (x - NA * KPAD);
+                        if (jv < V) val = ld_f(v + row * ld_v + h * V + jv);
                     }
-                } else {
-                    const int jv = blockIdx.x * VT + (x - NA * KPAD);
-                    if (jv < V) val = ld_f(v + row * ld_v + h * V + jv);
                 }
+                pre[tt * NPT + i] = val;
             }
-            pre[i] = val;
         }
     };
     fetch(r0, min(CT, r1 - r0));
@@ -221,32 +217,26 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
         const int n = min(CT, r1 - c0);
         __syncthreads();                     // the tokens staged before have been used
 #pragma unroll
-        for (int i = 0; i < VOB_SCAN_PRE; ++i) {
-            const int e = tid + i * nthr;
-            if (e < n * per_token) {
-                const int tt = e / per_token, x = e - tt * per_token;
-                if (x < NA * KPAD) {
-                    const int a = x / KPAD, c = x - a * KPAD;
-                    float* dst = a == 0 ? sr : a == 1 ? sk : a == 2 ? sw : a == 3 ? sb : su;
-                    dst[tt * KPAD + c] = pre[i];
-                } else {
-                    sv[tt * VT + (x - NA * KPAD)] = pre[i];
-                }
+        for (int tt = 0; tt < CT; ++tt)
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int x = tid + i * 128;
+                if (x < PER) sm[tt * PER + x] = pre[tt * NPT + i];
             }
-        }
         __syncthreads();
         if (c0 + CT < r1) fetch(c0 + CT, min(CT, r1 - c0 - CT));
         for (int tt = 0; tt < n; ++tt) {
-            const float* pr = sr + tt * KPAD + q;
-            const float* pk = sk + tt * KPAD + q;
-            const float vj = sv[tt * VT + jj];
+            const float* pr = sm + tt * PER + q;
+            const float* pk = pr + KPAD;
+            const float vj = sm[tt * PER + NA * KPAD + jj];
             if (MODE == 0) {
-                const float* pw = sw + tt * KPAD + q;
-                const float* pb = sb + tt * KPAD + q;
-                const float* pu = su + tt * KPAD + q;
+                const float* pw = pr + 2 * KPAD;
+                const float* pb = pr + 3 * KPAD;
+                const float* pu = pr + 4 * KPAD;
                 float dot = 0.f;
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) dot = fmaf(pu[i * KS], S[i], dot);
+#pragma unroll
                 for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(pk[i * KS], vj, fmaf(pw[i * KS], S[i], -(pb[i * KS] * dot)));
@@ -257,6 +247,7 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < KPT; ++i) acc = fmaf(pr[i * KS], S[i], acc);
+#pragma unroll
             for (int off = 1; off < KS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             if (q == 0 && col) o[(size_t)(c0 + tt) * H * V + h * V + j] = acc;
         }
@@ -268,34 +259,21 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     }
 }
 
-// How the key channels are shared out: KS lanes per column (a power of two), KPT registers per lane.
-static inline void scan_split(int K, int* KS, int* KPT) {
-    int ks = K <= 64 ? 4 : K <= 128 ? 8 : K <= 256 ? 16 : 32;
-    int per = (K + ks - 1) / ks;
-    *KS = ks;
-    *KPT = per <= 8 ? 8 : 16;           // K <= 512: at most 16 state registers per lane
-}
-
+// How the key channels are shared out: KS lanes per column (a power of two) with KPT state registers each:
+// K <= 32: 4 x 8; <= 64: 4 x 16; <= 128: 8 x 16; <= 256: 16 x 16; <= 512: 32 x 16.
 template <int MODE, typename TRK, typename TV>
 static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const void* v, long ld_v, const float* w, const float* b,
                        const float* u, float* state, const int* seq_starts, const int* state_slots, float* o, int seqs, int H, int K,
                        int V, cudaStream_t stream) {
-    int KS, KPT;
-    scan_split(K, &KS, &KPT);
-    const int VT = 128 / KS;
-    const int KPAD = KS * KPT;
-    const size_t per_token = (size_t)((MODE == 0 ? 5 : 2) * KPAD + VT) * 4;
-    // tokens staged at a time: what the block's 128 threads can hold of the next ones in VOB_SCAN_PRE registers each
-    int CT = (int)((size_t)VOB_SCAN_PRE * 128 * 4 / per_token);
-    CT = CT > 16 ? 16 : CT;
-    if (CT < 1) return VOB_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(5 * KPAD + VT) * 4 * CT;
-    dim3 grid((V + VT - 1) / VT, H, seqs), block(VT * KS);
-#define VOB_SCAN(P)                                                                                                            \
-    return vob_launch(recurrence_scan_kernel<MODE, P, TRK, TV>, grid, block, smem, stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, \
-                      (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, H, K, V, KS, VT, CT)
-    if (KPT == 8) VOB_SCAN(8);
-    VOB_SCAN(16);
+#define VOB_SCAN(P, KS_)                                                                                                        \
+    return vob_launch(recurrence_scan_kernel<MODE, P, KS_, TRK, TV>, dim3((V + 128 / KS_ - 1) / (128 / KS_), H, seqs), dim3(128), 0,  \
+                      stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, \
+                      H, K, V)
+    if (K <= 32) VOB_SCAN(8, 4);
+    if (K <= 64) VOB_SCAN(16, 4);
+    if (K <= 128) VOB_SCAN(16, 8);
+    if (K <= 256) VOB_SCAN(16, 16);
+    VOB_SCAN(16, 32);
 #undef VOB_SCAN
 }
 

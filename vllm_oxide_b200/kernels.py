@@ -909,6 +909,43 @@ def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, k
              out.stride(0), out.stride(1), splits, _ptr(partials) if splits > 1 else _P(0), _stream()), op, 2 if splits > 1 else 1)
 
 
+def latent_attend_tc_supported(heads: int, rank: int, rot: int) -> bool:
+    """Whether the tensor-core kernel for prompt portions takes these sizes (bfloat16 only)."""
+    f = _fn("latent_attention", "vob_latent_attend_tc_supported", [_I, _I, _I])
+    return bool(f(int(heads), int(rank), int(rot)))
+
+
+@_timed
+def latent_attend_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, kr: torch.Tensor, block_tables: torch.Tensor,
+                     seq_starts: torch.Tensor, positions: torch.Tensor, num_seqs: int, max_new: int, scale: float, out: torch.Tensor) -> None:
+    """`latent_attend` for prompt portions in bfloat16 on the tensor cores: request s owns rows seq_starts[s] ..
+    seq_starts[s + 1] - 1 (consecutive positions), none more than `max_new`. Same operands and result."""
+    op = "latent_attend_tc"
+    _cuda(op, q_lat, q_rot, lat, kr, block_tables, seq_starts, positions, out)
+    if q_lat.dim() != 3 or q_lat.dtype != torch.float32 or q_lat.stride(2) != 1:
+        raise ShapeError(op, f"q_lat must be float32 [T, heads, rank] with unit inner stride, got {q_lat.dtype} {list(q_lat.shape)}")
+    T, H, L = q_lat.shape
+    R = kr.shape[3]
+    if lat.dtype != torch.bfloat16 or kr.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise ShapeError(op, "the caches and out must be bfloat16")
+    if out.shape != (T, H, L) or out.stride(2) != 1:
+        raise ShapeError(op, f"out must be [{T}, {H}, {L}] with unit inner stride, got {list(out.shape)}")
+    if q_rot.shape != (T, H, R) or q_rot.dtype != torch.float32 or not q_rot.is_contiguous():
+        raise ShapeError(op, f"q_rot must be contiguous float32 [{T}, {H}, {R}], got {q_rot.dtype} {list(q_rot.shape)}")
+    if lat.dim() != 4 or lat.shape[1] != 1 or lat.shape[3] != L or kr.shape[:3] != lat.shape[:3] or not lat.is_contiguous() or not kr.is_contiguous():
+        raise ShapeError(op, f"lat [pages, 1, page, {L}] and kr [pages, 1, page, {R}] are needed, got {list(lat.shape)} and {list(kr.shape)}")
+    if not latent_attend_tc_supported(H, L, R):
+        raise ShapeError(op, f"a latent of {L} with a rotated part of {R} is not supported (multiples of 16 that fit shared memory)")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous() or block_tables.shape[0] < num_seqs:
+        raise ShapeError(op, "block_tables must be contiguous int32 [requests, max_pages]")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(positions, T, op, "positions")
+    f = _fn("latent_attention", "vob_latent_attend_tc", [_P, _L, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _L, _L, _P])
+    _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _ptr(block_tables), block_tables.shape[1],
+             _ptr(seq_starts), _ptr(positions), lat.shape[2], int(num_seqs), int(max_new), H, L, R, float(scale), _ptr(out), out.stride(0),
+             out.stride(1), _stream()), op)
+
+
 # ------------------------------------------------------------------------------------ attention
 @_timed
 def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,

@@ -47,6 +47,8 @@ class LatentAttention(Mixer):
         self.batched = True       # bfloat16: the per-head products as one batched library product (False: one by one, tests)
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
         self.splits = None        # a number forces so many blocks per row's keys (tests)
+        self.tensor_cores = True  # False: prompt portions go through the float32 kernel too (tests)
+        self._tc_ok = None
 
     def key_splits(self, rows: int) -> int:
         """Blocks that share a row's keys: steps of few rows would leave most of the GPU idle with one
@@ -93,8 +95,15 @@ class LatentAttention(Mixer):
             q_lat = ctx.alloc((H, T, L), torch.float32)
             torch.bmm(q_heads.transpose(0, 1), self.w_qlat.transpose(1, 2), out_dtype=torch.float32, out=q_lat)
             out_lat = ctx.alloc((H, T, L))
-            kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat.transpose(0, 1),
-                                  splits, partials)
+            if self._tc_ok is None:
+                self._tc_ok = kernels.latent_attend_tc_supported(H, L, R)
+            if self.tensor_cores and self._tc_ok and not ctx.decode_only and ctx.max_new > 1:
+                # prompt portions: scores and the weighted sum on the tensor cores, 16 tokens of a request at a time
+                kernels.latent_attend_tc(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.seq_starts, ctx.positions, ctx.seqs,
+                                         min(ctx.max_new, T), self.scale, out_lat.transpose(0, 1))
+            else:
+                kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale,
+                                      out_lat.transpose(0, 1), splits, partials)
             vals = ctx.alloc((H, T, V))
             torch.bmm(out_lat, self.w_val.transpose(1, 2), out=vals)
             attn = ctx.alloc((T, H * V))
