@@ -278,15 +278,15 @@ VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const
 
 // ---------------------------------------------------------------------------------------------
 // Prompt portions in bfloat16 on the tensor cores (mma.sync through the wmma interface). A block takes 16
-// consecutive tokens of one request and up to 4 heads, one warp per head; a tile of 32 keys ([c | kr], L + R
-// wide) is brought into shared memory once for all of them. Per warp and key tile: S = Q K^T (float32
+// consecutive tokens of one request and up to 4 heads, two warps per head; a tile of 32 keys ([c | kr], L + R
+// wide) is brought into shared memory once for all of them. Per head and key tile: S = Q K^T (float32
 // accumulation), the softmax of its 16 rows in float32 with the running maximum and sum in registers, P in
 // bfloat16, O += P C with O in shared memory as float32 (rescaled row by row when a maximum moves).
 // Needs L and R multiples of 16. Rows are a request's seq_starts[s] + 16 * tile .. ; their positions are
 // consecutive, so the tile's last row bounds the keys and every row masks what lies behind its own position.
 // ---------------------------------------------------------------------------------------------
 #define VOB_LTC_BN 32
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(256, 1)
 latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                         const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ kr, const int* __restrict__ block_tables,
                         int max_pages, const int* __restrict__ seq_starts, const int* __restrict__ positions, int page_size, int H, int L,
@@ -295,9 +295,12 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
     constexpr int BN = VOB_LTC_BN;
     pdl_launch_dependents();
     pdl_wait(48);
-    const int s = blockIdx.z, HB = blockDim.x >> 5;
+    // two warps per head: each computes one 16-key half of S, owns eight of the 16 rows in the softmax and half of
+    // the latent columns in O += P C. The phases are separated by block barriers that every warp passes.
+    const int s = blockIdx.z, HB = blockDim.x >> 6, NW = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y * HB + warp;
+    const int hh = warp >> 1, half = warp & 1;
+    const int h = blockIdx.y * HB + hh;
     const bool head = h < H;
     const int r0 = seq_starts[s] + blockIdx.x * 16, r1 = seq_starts[s + 1];
     if (r0 >= r1) return;
@@ -308,28 +311,29 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
     constexpr int LS = BN + 4, LP = BN + 8;
     extern __shared__ __align__(128) unsigned char ltc_smem[];
     __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(ltc_smem);                               // [BN][DP]
-    __nv_bfloat16* Q = Kt + (size_t)BN * DP + (size_t)warp * 16 * DP;                              // [16][DP] per warp
+    __nv_bfloat16* Q = Kt + (size_t)BN * DP + (size_t)hh * 16 * DP;                                // [16][DP] per head
     float* obase = reinterpret_cast<float*>(Kt + (size_t)BN * DP + (size_t)HB * 16 * DP);
-    float* O = obase + (size_t)warp * 16 * LO;                                                     // [16][LO] per warp
-    float* S = obase + (size_t)HB * 16 * LO + warp * 16 * LS;                                      // [16][LS] per warp
-    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(obase + (size_t)HB * 16 * LO + HB * 16 * LS) + warp * 16 * LP;
-    for (int e = lane; e < 16 * D; e += 32) {
+    float* O = obase + (size_t)hh * 16 * LO;                                                       // [16][LO] per head
+    float* S = obase + (size_t)HB * 16 * LO + hh * 16 * LS;                                        // [16][LS] per head
+    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(obase + (size_t)HB * 16 * LO + HB * 16 * LS) + hh * 16 * LP;
+    for (int e = lane + 32 * half; e < 16 * D; e += 64) {
         const int i = e / D, c = e - i * D;
         float v = 0.f;
         if (head && i < nrows)
             v = c < L ? q_lat[(size_t)(r0 + i) * q_ts + (size_t)h * q_hs + c] : q_rot[((size_t)(r0 + i) * H + h) * R + (c - L)];
         Q[i * DP + c] = __float2bfloat16_rn(v);
     }
-    for (int e = lane; e < 16 * LO; e += 32) O[e] = 0.f;
+    for (int e = lane + 32 * half; e < 16 * LO; e += 64) O[e] = 0.f;
     const int pos0 = positions[r0], pos_hi = pos0 + nrows - 1;
     const int* table = block_tables + (size_t)s * max_pages;
-    float m[16], l[16];
+    float m[8], l[8];                   // of rows 8 * half .. 8 * half + 7
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
+    for (int i = 0; i < 8; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
     const int lat_chunks = L / 8, kr_chunks = R / 8;            // 16-byte pieces of a key
+    const int ntiles = L / 16;
     for (int k0 = 0; k0 <= pos_hi; k0 += BN) {
         __syncthreads();
-        for (int kk = warp; kk < BN; kk += HB) {
+        for (int kk = warp; kk < BN; kk += NW) {
             const int key = k0 + kk;
             uint4* dst = reinterpret_cast<uint4*>(Kt + (size_t)kk * DP);
             if (key <= pos_hi) {
@@ -343,60 +347,64 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
             }
         }
         __syncthreads();
-        if (!head) continue;
-        // S = Q K^T
-#pragma unroll
-        for (int nt = 0; nt < BN / 16; ++nt) {
+        if (head) {
+            // S = Q K^T, this warp's 16 keys
             wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
             wmma::fill_fragment(c, 0.f);
             for (int ks = 0; ks < D / 16; ++ks) {
                 wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
                 wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
                 wmma::load_matrix_sync(a, Q + ks * 16, DP);
-                wmma::load_matrix_sync(b, Kt + (size_t)nt * 16 * DP + ks * 16, DP);
+                wmma::load_matrix_sync(b, Kt + (size_t)half * 16 * DP + ks * 16, DP);
                 wmma::mma_sync(c, a, b, c);
             }
-            wmma::store_matrix_sync(S + nt * 16, c, LS, wmma::mem_row_major);
+            wmma::store_matrix_sync(S + half * 16, c, LS, wmma::mem_row_major);
         }
-        __syncwarp();
-        // the softmax of the warp's 16 rows, one key per lane
-        const int key = k0 + lane;
+        __syncthreads();
+        if (head) {
+            // the softmax of this warp's eight rows, one key per lane
+            const int key = k0 + lane;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float sc = S[i * LS + lane] * scale;
-            if (i >= nrows || key > pos0 + i) sc = -INFINITY;
-            const float mn = fmaxf(m[i], warp_max(sc));
-            const bool none = mn == -INFINITY;
-            const float p = none ? 0.f : expf(sc - mn);
-            const float corr = none ? 1.f : expf(m[i] - mn);
-            l[i] = fmaf(l[i], corr, warp_sum(p));
-            m[i] = mn;
-            P[i * LP + lane] = __float2bfloat16_rn(p);
-            if (corr != 1.f)
-                for (int c = lane; c < L; c += 32) O[i * LO + c] *= corr;
-        }
-        __syncwarp();
-        // O += P C
-        for (int nt = 0; nt < L / 16; ++nt) {
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-            wmma::load_matrix_sync(c, O + nt * 16, LO, wmma::mem_row_major);
-#pragma unroll
-            for (int ks = 0; ks < BN / 16; ++ks) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::row_major> b;
-                wmma::load_matrix_sync(a, P + ks * 16, LP);
-                wmma::load_matrix_sync(b, Kt + (size_t)ks * 16 * DP + nt * 16, DP);
-                wmma::mma_sync(c, a, b, c);
+            for (int ii = 0; ii < 8; ++ii) {
+                const int i = 8 * half + ii;
+                float sc = S[i * LS + lane] * scale;
+                if (i >= nrows || key > pos0 + i) sc = -INFINITY;
+                const float mn = fmaxf(m[ii], warp_max(sc));
+                const bool none = mn == -INFINITY;
+                const float p = none ? 0.f : expf(sc - mn);
+                const float corr = none ? 1.f : expf(m[ii] - mn);
+                l[ii] = fmaf(l[ii], corr, warp_sum(p));
+                m[ii] = mn;
+                P[i * LP + lane] = __float2bfloat16_rn(p);
+                if (corr != 1.f)
+                    for (int c = lane; c < L; c += 32) O[i * LO + c] *= corr;
             }
-            wmma::store_matrix_sync(O + nt * 16, c, LO, wmma::mem_row_major);
         }
-        __syncwarp();
+        __syncthreads();
+        if (head) {
+            // O += P C, this warp's half of the latent columns
+            for (int nt = half; nt < ntiles; nt += 2) {
+                wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
+                wmma::load_matrix_sync(c, O + nt * 16, LO, wmma::mem_row_major);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
+                    wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::row_major> b;
+                    wmma::load_matrix_sync(a, P + ks * 16, LP);
+                    wmma::load_matrix_sync(b, Kt + (size_t)ks * 16 * DP + nt * 16, DP);
+                    wmma::mma_sync(c, a, b, c);
+                }
+                wmma::store_matrix_sync(O + nt * 16, c, LO, wmma::mem_row_major);
+            }
+        }
     }
+    __syncthreads();
     if (!head) return;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int ii = 0; ii < 8; ++ii) {
+        const int i = 8 * half + ii;
         if (i < nrows) {
-            const float inv = 1.0f / l[i];
+            const float inv = 1.0f / l[ii];
             __nv_bfloat16* orow = out + (size_t)(r0 + i) * o_ts + (size_t)h * o_hs;
             for (int c = lane; c < L; c += 32) orow[c] = __float2bfloat16_rn(O[i * LO + c] * inv);
         }
@@ -410,7 +418,9 @@ static int ltc_heads(int H, int L, int R) {
     const size_t shared = (size_t)VOB_LTC_BN * DP * 2;
     const size_t per_head = 16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2;
     if (shared + per_head > 200 * 1024) return 0;
-    int hb = (int)((200 * 1024 - shared) / per_head);
+    // as many heads as let two blocks share an SM (one block brings its keys in while the other computes) if that
+    // is at least two; else as many as fit one block (a key tile read for a single head is read too often)
+    int hb = shared + 2 * per_head > 100 * 1024 ? (int)((200 * 1024 - shared) / per_head) : (int)((100 * 1024 - shared) / per_head);
     hb = hb > 4 ? 4 : hb;
     return hb > H ? H : hb;
 }
@@ -432,7 +442,7 @@ VOB_EXPORT int vob_latent_attend_tc(const float* q_lat, long q_ts, long q_hs, co
         + (size_t)hb * (16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2);
     cudaError_t e = cudaFuncSetAttribute(latent_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return vob_launch(latent_attend_tc_kernel, dim3((max_new + 15) / 16, (H + hb - 1) / hb, seqs), dim3(32 * hb), smem, stream, q_lat, q_ts,
+    return vob_launch(latent_attend_tc_kernel, dim3((max_new + 15) / 16, (H + hb - 1) / hb, seqs), dim3(64 * hb), smem, stream, q_lat, q_ts,
                       q_hs, q_rot, (const __nv_bfloat16*)lat, (const __nv_bfloat16*)kr, block_tables, max_pages, seq_starts, positions,
                       page_size, H, L, R, scale, (__nv_bfloat16*)out, o_ts, o_hs);
 }

@@ -9,7 +9,7 @@
 //
 // Every value column of S evolves on its own, so the work is cut by columns: a block owns VT
 // columns of one head of one request, KS threads share a column (thread q of them holds key
-// channels q, q + KS, ... in registers) and the two dot products over key channels are finished
+// channels q * KPT .. q * KPT + KPT - 1 in registers) and the two dot products over key channels are finished
 // by shuffles among those KS lanes, in a fixed order. The block walks the request's rows of this
 // step in order, a few tokens at a time staged in shared memory. A step of one token is the same
 // kernel: read the state, one update, write it back (bound by the state's bytes). The arithmetic
@@ -22,6 +22,14 @@
 VOB_PDL_SWITCH(recurrence)
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// An element as its raw bits, and back: a value fetched ahead stays untouched in its register until it is
+// used (a conversion right behind the load would make the warp wait for the load there and then).
+__device__ __forceinline__ unsigned raw_ld(const float* p) { return __float_as_uint(*p); }
+__device__ __forceinline__ unsigned raw_ld(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned short*>(p); }
+template <typename T> __device__ __forceinline__ float raw_to_float(unsigned x);
+template <> __device__ __forceinline__ float raw_to_float<float>(unsigned x) { return __uint_as_float(x); }
+template <> __device__ __forceinline__ float raw_to_float<__nv_bfloat16>(unsigned x) { return __uint_as_float(x << 16); }
 
 // ---------------------------------------------------------------------------------------------
 // Delta-rule preparation, per token t, head h and key channel c (ch = h * K + c):
@@ -166,14 +174,18 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     // t takes elements t, t + 128, ... of it (NPT per token), and the list of the next CT tokens is fetched into
     // registers while the staged tokens are worked on. The chain from token to token is what bounds a long portion.
     constexpr int KPAD = KS * KPT, VT = 128 / KS, NA = MODE == 0 ? 5 : 2;
-    constexpr int PER = NA * KPAD + VT, NPT = (PER + 127) / 128;
+    // Lane q of a column holds key channels q * KPT .. q * KPT + KPT - 1. In shared memory a lane's channels lie
+    // together (read four at a time), each lane's group padded by four floats so that the KS groups fall into
+    // different banks: channel c of an array at (c / KPT) * (KPT + 4) + c % KPT.
+    constexpr int GRP = KPT + 4, KPADP = KS * GRP;
+    constexpr int PER = NA * KPADP + VT, NPT = (NA * KPAD + VT + 127) / 128;
     constexpr int CT = NPT >= 24 ? 1 : (24 / NPT > 8 ? 8 : 24 / NPT);
     pdl_launch_dependents();
     pdl_wait(43);
     const int s = blockIdx.z, h = blockIdx.y;
     const int r0 = seq_starts[s], r1 = seq_starts[s + 1];
     if (r1 <= r0) return;
-    __shared__ float sm[CT * PER];           // token tt: [r | k | (w | b | u) | v] at sm + tt * PER
+    __shared__ __align__(16) float sm[CT * PER];     // token tt: [r | k | (w | b | u) | v] at sm + tt * PER
     const int tid = threadIdx.x;
     const int q = tid % KS, jj = tid / KS;
     const int j = blockIdx.x * VT + jj;
@@ -182,11 +194,11 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     float S[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
-        const int c = q + i * KS;
+        const int c = q * KPT + i;
         S[i] = (col && c < K) ? S_glob[(size_t)c * V + j] : 0.f;
     }
     const float decay = MODE == 1 ? w[h] : 0.f;
-    float pre[CT * NPT];
+    unsigned pre[CT * NPT];              // raw bits: converted when they are staged, not when they arrive
     auto fetch = [&](int c0, int n) {
 #pragma unroll
         for (int tt = 0; tt < CT; ++tt) {
@@ -194,18 +206,18 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
 #pragma unroll
             for (int i = 0; i < NPT; ++i) {
                 const int x = tid + i * 128;            // which array and channel x is does not depend on the token
-                float val = 0.f;
-                if (tt < n && x < PER) {
+                unsigned val = 0u;                      // the bits of 0 in either type
+                if (tt < n && x < NA * KPAD + VT) {
                     if (x < NA * KPAD) {
                         const int a = x / KPAD, c = x % KPAD;
                         if (c < K) {
                             const size_t g = row * H * K + h * K + c;
-                            val = a == 0 ? ld_f(r + row * ld_r + h * K + c) : a == 1 ? ld_f(k + row * ld_k + h * K + c)
-                                : a == 2 ? w[g] : a == 3 ? b[g] : u[g];
+                            val = a == 0 ? raw_ld(r + row * ld_r + h * K + c) : a == 1 ? raw_ld(k + row * ld_k + h * K + c)
+                                : a == 2 ? raw_ld(w + g) : a == 3 ? raw_ld(b + g) : raw_ld(u + g);
                         }
                     } else {
                         const int jv = blockIdx.x * VT + (x - NA * KPAD);
-                        if (jv < V) val = ld_f(v + row * ld_v + h * V + jv);
+                        if (jv < V) val = raw_ld(v + row * ld_v + h * V + jv);
                     }
                 }
                 pre[tt * NPT + i] = val;
@@ -221,32 +233,65 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
 #pragma unroll
             for (int i = 0; i < NPT; ++i) {
                 const int x = tid + i * 128;
-                if (x < PER) sm[tt * PER + x] = pre[tt * NPT + i];
+                if (x < NA * KPAD) {
+                    const int a = x / KPAD, c = x % KPAD;
+                    sm[tt * PER + a * KPADP + (c / KPT) * GRP + c % KPT] =
+                        a < 2 ? raw_to_float<TRK>(pre[tt * NPT + i]) : __uint_as_float(pre[tt * NPT + i]);
+                } else if (x < NA * KPAD + VT) {
+                    sm[tt * PER + NA * KPADP + (x - NA * KPAD)] = raw_to_float<TV>(pre[tt * NPT + i]);
+                }
             }
         __syncthreads();
         if (c0 + CT < r1) fetch(c0 + CT, min(CT, r1 - c0 - CT));
         for (int tt = 0; tt < n; ++tt) {
-            const float* pr = sm + tt * PER + q;
-            const float* pk = pr + KPAD;
-            const float vj = sm[tt * PER + NA * KPAD + jj];
-            if (MODE == 0) {
-                const float* pw = pr + 2 * KPAD;
-                const float* pb = pr + 3 * KPAD;
-                const float* pu = pr + 4 * KPAD;
-                float dot = 0.f;
+            const float4* pr = reinterpret_cast<const float4*>(sm + tt * PER + q * GRP);
+            const float4* pk = reinterpret_cast<const float4*>(sm + tt * PER + KPADP + q * GRP);
+            const float vj = sm[tt * PER + NA * KPADP + jj];
+            float rr[KPT], kk[KPT];
 #pragma unroll
-                for (int i = 0; i < KPT; ++i) dot = fmaf(pu[i * KS], S[i], dot);
+            for (int i = 0; i < KPT / 4; ++i) {
+                const float4 a = pr[i], c = pk[i];
+                rr[4 * i] = a.x; rr[4 * i + 1] = a.y; rr[4 * i + 2] = a.z; rr[4 * i + 3] = a.w;
+                kk[4 * i] = c.x; kk[4 * i + 1] = c.y; kk[4 * i + 2] = c.z; kk[4 * i + 3] = c.w;
+            }
+            if (MODE == 0) {
+                const float4* pw = reinterpret_cast<const float4*>(sm + tt * PER + 2 * KPADP + q * GRP);
+                const float4* pb = reinterpret_cast<const float4*>(sm + tt * PER + 3 * KPADP + q * GRP);
+                const float4* pu = reinterpret_cast<const float4*>(sm + tt * PER + 4 * KPADP + q * GRP);
+                // four partial sums: the chain of dependent additions is a quarter as long; their order is fixed
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT / 4; ++i) {
+                    const float4 uu = pu[i];
+                    d0 = fmaf(uu.x, S[4 * i], d0);
+                    d1 = fmaf(uu.y, S[4 * i + 1], d1);
+                    d2 = fmaf(uu.z, S[4 * i + 2], d2);
+                    d3 = fmaf(uu.w, S[4 * i + 3], d3);
+                }
+                float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
                 for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
 #pragma unroll
-                for (int i = 0; i < KPT; ++i) S[i] = fmaf(pk[i * KS], vj, fmaf(pw[i * KS], S[i], -(pb[i * KS] * dot)));
+                for (int i = 0; i < KPT / 4; ++i) {
+                    const float4 ww = pw[i], bb = pb[i];
+                    S[4 * i] = fmaf(kk[4 * i], vj, fmaf(ww.x, S[4 * i], -(bb.x * dot)));
+                    S[4 * i + 1] = fmaf(kk[4 * i + 1], vj, fmaf(ww.y, S[4 * i + 1], -(bb.y * dot)));
+                    S[4 * i + 2] = fmaf(kk[4 * i + 2], vj, fmaf(ww.z, S[4 * i + 2], -(bb.z * dot)));
+                    S[4 * i + 3] = fmaf(kk[4 * i + 3], vj, fmaf(ww.w, S[4 * i + 3], -(bb.w * dot)));
+                }
             } else {
 #pragma unroll
-                for (int i = 0; i < KPT; ++i) S[i] = fmaf(pk[i * KS], vj, decay * S[i]);
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], vj, decay * S[i]);
             }
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < KPT; ++i) acc = fmaf(pr[i * KS], S[i], acc);
+            for (int i = 0; i < KPT / 4; ++i) {
+                a0 = fmaf(rr[4 * i], S[4 * i], a0);
+                a1 = fmaf(rr[4 * i + 1], S[4 * i + 1], a1);
+                a2 = fmaf(rr[4 * i + 2], S[4 * i + 2], a2);
+                a3 = fmaf(rr[4 * i + 3], S[4 * i + 3], a3);
+            }
+            float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
             for (int off = 1; off < KS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             if (q == 0 && col) o[(size_t)(c0 + tt) * H * V + h * V + j] = acc;
@@ -254,7 +299,7 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     }
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
-        const int c = q + i * KS;
+        const int c = q * KPT + i;
         if (col && c < K) S_glob[(size_t)c * V + j] = S[i];
     }
 }
