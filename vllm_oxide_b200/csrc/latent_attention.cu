@@ -286,6 +286,7 @@ VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const
 // consecutive, so the tile's last row bounds the keys and every row masks what lies behind its own position.
 // ---------------------------------------------------------------------------------------------
 #define VOB_LTC_BN 32
+#define VOB_LTC_PRE 10        // 16-byte pieces of the next key tile a thread holds ahead (the rest of a tile is copied when it is due)
 __global__ void __launch_bounds__(256, 1)
 latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                         const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ kr, const int* __restrict__ block_tables,
@@ -331,21 +332,52 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
     for (int i = 0; i < 8; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
     const int lat_chunks = L / 8, kr_chunks = R / 8;            // 16-byte pieces of a key
     const int ntiles = L / 16;
+    // The key tile as a list of 16-byte pieces, BN keys x (lat_chunks + kr_chunks) pieces: thread t takes pieces
+    // t, t + 256, ... The NEXT tile's pieces are fetched into registers while this tile is worked on.
+    const int pieces = lat_chunks + kr_chunks, tile_pieces = BN * pieces;
+    const int dp_pieces = DP / 8;                    // a row of Kt in 16-byte pieces (DP is a multiple of 8)
+    uint4 nxt[VOB_LTC_PRE];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < VOB_LTC_PRE; ++i) {
+            const int x = (int)threadIdx.x + i * (int)blockDim.x;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (x < tile_pieces) {
+                const int kk = x / pieces, c = x - kk * pieces;
+                const int key = k0 + kk;
+                if (key <= pos_hi) {
+                    const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
+                    val = c < lat_chunks ? reinterpret_cast<const uint4*>(lat + slot * L)[c]
+                                         : reinterpret_cast<const uint4*>(kr + slot * R)[c - lat_chunks];
+                }
+            }
+            nxt[i] = val;
+        }
+    };
+    fetch(0);
     for (int k0 = 0; k0 <= pos_hi; k0 += BN) {
         __syncthreads();
-        for (int kk = warp; kk < BN; kk += NW) {
-            const int key = k0 + kk;
-            uint4* dst = reinterpret_cast<uint4*>(Kt + (size_t)kk * DP);
-            if (key <= pos_hi) {
-                const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
-                const uint4* a = reinterpret_cast<const uint4*>(lat + slot * L);
-                const uint4* b = reinterpret_cast<const uint4*>(kr + slot * R);
-                for (int c = lane; c < lat_chunks; c += 32) dst[c] = a[c];
-                for (int c = lane; c < kr_chunks; c += 32) dst[lat_chunks + c] = b[c];
-            } else {
-                for (int c = lane; c < lat_chunks + kr_chunks; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < VOB_LTC_PRE; ++i) {
+            const int x = (int)threadIdx.x + i * (int)blockDim.x;
+            if (x < tile_pieces) {
+                const int kk = x / pieces, c = x - kk * pieces;
+                reinterpret_cast<uint4*>(Kt)[(size_t)kk * dp_pieces + c] = nxt[i];
             }
         }
+        // what of a tile the registers do not hold (small blocks, wide keys) is copied now
+        for (int x = (int)threadIdx.x + VOB_LTC_PRE * (int)blockDim.x; x < tile_pieces; x += (int)blockDim.x) {
+            const int kk = x / pieces, c = x - kk * pieces;
+            const int key = k0 + kk;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (key <= pos_hi) {
+                const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
+                val = c < lat_chunks ? reinterpret_cast<const uint4*>(lat + slot * L)[c]
+                                     : reinterpret_cast<const uint4*>(kr + slot * R)[c - lat_chunks];
+            }
+            reinterpret_cast<uint4*>(Kt)[(size_t)kk * dp_pieces + c] = val;
+        }
+        if (k0 + BN <= pos_hi) fetch(k0 + BN);
         __syncthreads();
         if (head) {
             // S = Q K^T, this warp's 16 keys
