@@ -17,7 +17,6 @@
 // puts together in a fixed order.
 #include "common.cuh"
 #include <math.h>
-#include <mma.h>
 VOB_PDL_SWITCH(latent_attention)
 
 // proj [T, ld]: the query of head h at columns q_off + h * (D + R) (D plain features, then R to be
@@ -277,63 +276,79 @@ VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const
 
 
 // ---------------------------------------------------------------------------------------------
-// Prompt portions in bfloat16 on the tensor cores (mma.sync through the wmma interface). A block takes 16
-// consecutive tokens of one request and up to 4 heads, two warps per head; a tile of 32 keys ([c | kr], L + R
-// wide) is brought into shared memory once for all of them. Per head and key tile: S = Q K^T (float32
-// accumulation), the softmax of its 16 rows in float32 with the running maximum and sum in registers, P in
-// bfloat16, O += P C with O in shared memory as float32 (rescaled row by row when a maximum moves).
-// Needs L and R multiples of 16. Rows are a request's seq_starts[s] + 16 * tile .. ; their positions are
-// consecutive, so the tile's last row bounds the keys and every row masks what lies behind its own position.
+// Prompt portions in bfloat16 on the tensor cores (mma.sync m16n8k16, operands by ldmatrix). A block takes 16
+// consecutive tokens of one request and HB heads; a head has WPH warps, each of which owns a share of the latent
+// columns of O (at most 256) and computes the head's S = Q K^T for itself. A tile of 32 keys ([c | kr], L + R
+// wide, bfloat16, rows padded by 16 bytes so that ldmatrix meets no bank conflict) is brought into shared memory
+// once for all of them; the next tile is fetched into registers meanwhile. S, the softmax (float32, running
+// maximum and sum per row), P (bfloat16, taken straight from S's registers as the next product's A operand) and
+// O (float32) never leave the registers. Needs L and R multiples of 16. Rows are a request's seq_starts[s] + 16
+// * tile ..; their positions are consecutive, so the tile's last row bounds the keys and every row masks what
+// lies behind its own position.
 // ---------------------------------------------------------------------------------------------
 #define VOB_LTC_BN 32
 #define VOB_LTC_PRE 10        // 16-byte pieces of the next key tile a thread holds ahead (the rest of a tile is copied when it is due)
+
+__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// NT16: groups of 16 latent columns a warp owns at most (its O accumulator is NT16 * 8 registers).
+template <int NT16>
 __global__ void __launch_bounds__(256, 1)
 latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                         const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ kr, const int* __restrict__ block_tables,
                         int max_pages, const int* __restrict__ seq_starts, const int* __restrict__ positions, int page_size, int H, int L,
-                        int R, float scale, __nv_bfloat16* __restrict__ out, long o_ts, long o_hs) {
-    using namespace nvcuda;
+                        int R, float scale, __nv_bfloat16* __restrict__ out, long o_ts, long o_hs, int WPH, int colsw) {
     constexpr int BN = VOB_LTC_BN;
     pdl_launch_dependents();
     pdl_wait(48);
-    // two warps per head: each computes one 16-key half of S, owns eight of the 16 rows in the softmax and half of
-    // the latent columns in O += P C. The phases are separated by block barriers that every warp passes.
-    const int s = blockIdx.z, HB = blockDim.x >> 6, NW = blockDim.x >> 5;
+    const int s = blockIdx.z, NW = blockDim.x >> 5, HB = NW / WPH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hh = warp >> 1, half = warp & 1;
+    const int hh = warp / WPH, wsub = warp - hh * WPH;
     const int h = blockIdx.y * HB + hh;
     const bool head = h < H;
     const int r0 = seq_starts[s] + blockIdx.x * 16, r1 = seq_starts[s + 1];
     if (r0 >= r1) return;
     const int nrows = min(16, r1 - r0);
-    const int D = L + R;
-    // leading dimensions with a few elements of padding: rows 512 or 1,024 bytes apart would all fall into the same banks
-    const int DP = D + 8, LO = L + 4;
-    constexpr int LS = BN + 4, LP = BN + 8;
+    const int D = L + R, DP = D + 8;
     extern __shared__ __align__(128) unsigned char ltc_smem[];
     __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(ltc_smem);                               // [BN][DP]
     __nv_bfloat16* Q = Kt + (size_t)BN * DP + (size_t)hh * 16 * DP;                                // [16][DP] per head
-    float* obase = reinterpret_cast<float*>(Kt + (size_t)BN * DP + (size_t)HB * 16 * DP);
-    float* O = obase + (size_t)hh * 16 * LO;                                                       // [16][LO] per head
-    float* S = obase + (size_t)HB * 16 * LO + hh * 16 * LS;                                        // [16][LS] per head
-    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(obase + (size_t)HB * 16 * LO + HB * 16 * LS) + hh * 16 * LP;
-    for (int e = lane + 32 * half; e < 16 * D; e += 64) {
+    for (int e = lane + 32 * wsub; e < 16 * D; e += 32 * WPH) {
         const int i = e / D, c = e - i * D;
         float v = 0.f;
         if (head && i < nrows)
             v = c < L ? q_lat[(size_t)(r0 + i) * q_ts + (size_t)h * q_hs + c] : q_rot[((size_t)(r0 + i) * H + h) * R + (c - L)];
         Q[i * DP + c] = __float2bfloat16_rn(v);
     }
-    for (int e = lane + 32 * half; e < 16 * LO; e += 64) O[e] = 0.f;
     const int pos0 = positions[r0], pos_hi = pos0 + nrows - 1;
     const int* table = block_tables + (size_t)s * max_pages;
-    float m[8], l[8];                   // of rows 8 * half .. 8 * half + 7
+    // this warp's latent columns, in groups of 16
+    const int col0 = wsub * colsw;
+    const int n16 = max(0, min(colsw, L - col0)) / 16;
+    const int g = lane >> 2, t4 = lane & 3;          // this thread's rows g and g + 8, columns 2 * t4, + 1 of every 8
+    float o[NT16 * 2][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
+    for (int i = 0; i < NT16 * 2; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // l: this thread's share of the row sums
+    const bool row0 = g < nrows, row1 = g + 8 < nrows;
     const int lat_chunks = L / 8, kr_chunks = R / 8;            // 16-byte pieces of a key
-    const int ntiles = L / 16;
     // The key tile as a list of 16-byte pieces, BN keys x (lat_chunks + kr_chunks) pieces: thread t takes pieces
-    // t, t + 256, ... The NEXT tile's pieces are fetched into registers while this tile is worked on.
+    // t, t + threads, ... The NEXT tile's pieces are fetched into registers while this tile is worked on.
     const int pieces = lat_chunks + kr_chunks, tile_pieces = BN * pieces;
     const int dp_pieces = DP / 8;                    // a row of Kt in 16-byte pieces (DP is a multiple of 8)
     uint4 nxt[VOB_LTC_PRE];
@@ -379,102 +394,145 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
         }
         if (k0 + BN <= pos_hi) fetch(k0 + BN);
         __syncthreads();
-        if (head) {
-            // S = Q K^T, this warp's 16 keys
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-            wmma::fill_fragment(c, 0.f);
-            for (int ks = 0; ks < D / 16; ++ks) {
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b;
-                wmma::load_matrix_sync(a, Q + ks * 16, DP);
-                wmma::load_matrix_sync(b, Kt + (size_t)half * 16 * DP + ks * 16, DP);
-                wmma::mma_sync(c, a, b, c);
-            }
-            wmma::store_matrix_sync(S + half * 16, c, LS, wmma::mem_row_major);
-        }
-        __syncthreads();
-        if (head) {
-            // the softmax of this warp's eight rows, one key per lane
-            const int key = k0 + lane;
+        if (!head) continue;
+        // S = Q K^T: 16 rows x 32 keys, four accumulator tiles of 8 keys
+        float sc[4][4];
 #pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-                const int i = 8 * half + ii;
-                float sc = S[i * LS + lane] * scale;
-                if (i >= nrows || key > pos0 + i) sc = -INFINITY;
-                const float mn = fmaxf(m[ii], warp_max(sc));
-                const bool none = mn == -INFINITY;
-                const float p = none ? 0.f : expf(sc - mn);
-                const float corr = none ? 1.f : expf(m[ii] - mn);
-                l[ii] = fmaf(l[ii], corr, warp_sum(p));
-                m[ii] = mn;
-                P[i * LP + lane] = __float2bfloat16_rn(p);
-                if (corr != 1.f)
-                    for (int c = lane; c < L; c += 32) O[i * LO + c] *= corr;
+        for (int j = 0; j < 4; ++j) { sc[j][0] = 0.f; sc[j][1] = 0.f; sc[j][2] = 0.f; sc[j][3] = 0.f; }
+#pragma unroll 2
+        for (int ks = 0; ks < D / 16; ++ks) {
+            unsigned a0, a1, a2, a3;
+            ldsm_x4(a0, a1, a2, a3, Q + (size_t)(lane & 15) * DP + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {            // keys 16 * jp .. + 15: two accumulator tiles
+                unsigned b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, Kt + (size_t)(16 * jp + (lane >> 4) * 8 + (lane & 7)) * DP + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(sc[2 * jp], a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(sc[2 * jp + 1], a0, a1, a2, a3, b2, b3);
             }
         }
-        __syncthreads();
-        if (head) {
-            // O += P C, this warp's half of the latent columns
-            for (int nt = half; nt < ntiles; nt += 2) {
-                wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-                wmma::load_matrix_sync(c, O + nt * 16, LO, wmma::mem_row_major);
+        // the softmax of rows g and g + 8 over this tile's keys
+        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> a;
-                    wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::row_major> b;
-                    wmma::load_matrix_sync(a, P + ks * 16, LP);
-                    wmma::load_matrix_sync(b, Kt + (size_t)ks * 16 * DP + nt * 16, DP);
-                    wmma::mma_sync(c, a, b, c);
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = k0 + 8 * j + 2 * t4 + e;
+                sc[j][e] = (row0 && key <= pos0 + g) ? sc[j][e] * scale : -INFINITY;
+                sc[j][2 + e] = (row1 && key <= pos0 + g + 8) ? sc[j][2 + e] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, sc[j][e]);
+                mx1 = fmaxf(mx1, sc[j][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const bool none0 = mn0 == -INFINITY, none1 = mn1 == -INFINITY;
+        const float corr0 = none0 ? 1.f : expf(m0 - mn0), corr1 = none1 ? 1.f : expf(m1 - mn1);
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                sc[j][e] = none0 ? 0.f : expf(sc[j][e] - mn0);
+                sc[j][2 + e] = none1 ? 0.f : expf(sc[j][2 + e] - mn1);
+                sum0 += sc[j][e];
+                sum1 += sc[j][2 + e];
+            }
+        }
+        l0 = fmaf(l0, corr0, sum0);
+        l1 = fmaf(l1, corr1, sum1);
+        m0 = mn0;
+        m1 = mn1;
+        // P as the A operand of the second product: the accumulator tiles of 8 keys pair up into 16 keys
+        unsigned pa[2][4];
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+            pa[jp][0] = pack_bf16(sc[2 * jp][0], sc[2 * jp][1]);
+            pa[jp][1] = pack_bf16(sc[2 * jp][2], sc[2 * jp][3]);
+            pa[jp][2] = pack_bf16(sc[2 * jp + 1][0], sc[2 * jp + 1][1]);
+            pa[jp][3] = pack_bf16(sc[2 * jp + 1][2], sc[2 * jp + 1][3]);
+        }
+        // O = O * corr + P C over this warp's latent columns
+#pragma unroll
+        for (int n = 0; n < NT16; ++n) {
+            if (n < n16) {
+                o[2 * n][0] *= corr0; o[2 * n][1] *= corr0; o[2 * n][2] *= corr1; o[2 * n][3] *= corr1;
+                o[2 * n + 1][0] *= corr0; o[2 * n + 1][1] *= corr0; o[2 * n + 1][2] *= corr1; o[2 * n + 1][3] *= corr1;
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp) {
+                    unsigned b0, b1, b2, b3;
+                    ldsm_x4_trans(b0, b1, b2, b3, Kt + (size_t)(16 * jp + ((lane >> 3) & 1) * 8 + (lane & 7)) * DP + col0 + 16 * n + (lane >> 4) * 8);
+                    mma_bf16_16816(o[2 * n], pa[jp][0], pa[jp][1], pa[jp][2], pa[jp][3], b0, b1);
+                    mma_bf16_16816(o[2 * n + 1], pa[jp][0], pa[jp][1], pa[jp][2], pa[jp][3], b2, b3);
                 }
-                wmma::store_matrix_sync(O + nt * 16, c, LO, wmma::mem_row_major);
             }
         }
     }
-    __syncthreads();
     if (!head) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
 #pragma unroll
-    for (int ii = 0; ii < 8; ++ii) {
-        const int i = 8 * half + ii;
-        if (i < nrows) {
-            const float inv = 1.0f / l[ii];
-            __nv_bfloat16* orow = out + (size_t)(r0 + i) * o_ts + (size_t)h * o_hs;
-            for (int c = lane; c < L; c += 32) orow[c] = __float2bfloat16_rn(O[i * LO + c] * inv);
+    for (int n = 0; n < NT16 * 2; ++n) {
+        if (n < 2 * n16) {
+            const int c = col0 + 8 * n + 2 * t4;
+            if (row0)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + g) * o_ts + (size_t)h * o_hs + c) = __floats2bfloat162_rn(o[n][0] * inv0, o[n][1] * inv0);
+            if (row1)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(r0 + g + 8) * o_ts + (size_t)h * o_hs + c) = __floats2bfloat162_rn(o[n][2] * inv1, o[n][3] * inv1);
         }
     }
 }
 
-// Heads a block of the tensor-core kernel takes (0: the sizes do not fit it).
-static int ltc_heads(int H, int L, int R) {
-    if (L % 16 || R % 16 || L <= 0 || R <= 0) return 0;
+// The shape of a block of the tensor-core kernel: warps per head (each with at most 256 latent columns, a multiple of
+// 16), the columns per warp, and heads per block (0: the sizes do not fit the kernel).
+static int ltc_shape(int H, int L, int R, int* wph, int* colsw) {
+    if (L % 16 || R % 16 || L <= 0 || R <= 0 || L > 1024) return 0;
+    *wph = (L + 255) / 256;
+    *colsw = ((L / 16 + *wph - 1) / *wph) * 16;
     const size_t DP = (size_t)L + R + 8;
-    const size_t shared = (size_t)VOB_LTC_BN * DP * 2;
-    const size_t per_head = 16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2;
-    if (shared + per_head > 200 * 1024) return 0;
-    // as many heads as let two blocks share an SM (one block brings its keys in while the other computes) if that
-    // is at least two; else as many as fit one block (a key tile read for a single head is read too often)
-    int hb = shared + 2 * per_head > 100 * 1024 ? (int)((200 * 1024 - shared) / per_head) : (int)((100 * 1024 - shared) / per_head);
-    hb = hb > 4 ? 4 : hb;
+    const size_t shared = (size_t)VOB_LTC_BN * DP * 2, per_head = 16 * DP * 2;
+    int hb = 8 / *wph;                                   // at most eight warps
+    while (hb > 1 && shared + hb * per_head > 100 * 1024) --hb;
+    if (shared + hb * per_head > 200 * 1024) return 0;
     return hb > H ? H : hb;
 }
 
-VOB_EXPORT int vob_latent_attend_tc_supported(int H, int L, int R) { return ltc_heads(H, L, R) > 0 ? 1 : 0; }
+VOB_EXPORT int vob_latent_attend_tc_supported(int H, int L, int R) {
+    int wph, colsw;
+    return ltc_shape(H, L, R, &wph, &colsw) > 0 ? 1 : 0;
+}
 
-// q_lat, q_rot, out and the caches as for vob_latent_attend (bfloat16 caches and out only); seq_starts int32
-// [seqs + 1]; max_new: no request brings more rows than this.
+// q_lat, q_rot, out and the caches as for vob_latent_attend (bfloat16 caches and out only; out's strides even);
+// seq_starts int32 [seqs + 1]; max_new: no request brings more rows than this.
 VOB_EXPORT int vob_latent_attend_tc(const float* q_lat, long q_ts, long q_hs, const float* q_rot, const void* lat, const void* kr,
                                     const int* block_tables, int max_pages, const int* seq_starts, const int* positions, int page_size,
                                     int seqs, int max_new, int H, int L, int R, float scale, void* out, long o_ts, long o_hs,
                                     cudaStream_t stream) {
     if (seqs <= 0 || max_new <= 0) return 0;
-    const int hb = ltc_heads(H, L, R);
+    int wph, colsw;
+    const int hb = ltc_shape(H, L, R, &wph, &colsw);
     if (hb <= 0) return VOB_ERR_UNSUPPORTED;
-    if (page_size <= 0 || max_pages <= 0 || seqs > 65535 || (H + hb - 1) / hb > 65535) return VOB_ERR_BAD_ARG;
+    if (page_size <= 0 || max_pages <= 0 || seqs > 65535 || (H + hb - 1) / hb > 65535 || (o_ts & 1) || (o_hs & 1) || ((uintptr_t)out & 3))
+        return VOB_ERR_BAD_ARG;
     const size_t DP = (size_t)L + R + 8;
-    const size_t smem = (size_t)VOB_LTC_BN * DP * 2
-        + (size_t)hb * (16 * DP * 2 + 16 * ((size_t)L + 4) * 4 + 16 * (VOB_LTC_BN + 4) * 4 + 16 * (VOB_LTC_BN + 8) * 2);
-    cudaError_t e = cudaFuncSetAttribute(latent_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    return vob_launch(latent_attend_tc_kernel, dim3((max_new + 15) / 16, (H + hb - 1) / hb, seqs), dim3(64 * hb), smem, stream, q_lat, q_ts,
-                      q_hs, q_rot, (const __nv_bfloat16*)lat, (const __nv_bfloat16*)kr, block_tables, max_pages, seq_starts, positions,
-                      page_size, H, L, R, scale, (__nv_bfloat16*)out, o_ts, o_hs);
+    const size_t smem = (size_t)VOB_LTC_BN * DP * 2 + (size_t)hb * 16 * DP * 2;
+    dim3 grid((max_new + 15) / 16, (H + hb - 1) / hb, seqs), block(32 * hb * wph);
+#define VOB_LTC(N)                                                                                                              \
+    do {                                                                                                                        \
+        cudaError_t e = cudaFuncSetAttribute(latent_attend_tc_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                                                    \
+        return vob_launch(latent_attend_tc_kernel<N>, grid, block, smem, stream, q_lat, q_ts, q_hs, q_rot, (const __nv_bfloat16*)lat, \
+                          (const __nv_bfloat16*)kr, block_tables, max_pages, seq_starts, positions, page_size, H, L, R, scale,  \
+                          (__nv_bfloat16*)out, o_ts, o_hs, wph, colsw);                                                         \
+    } while (0)
+    if (colsw <= 64) VOB_LTC(4);
+    if (colsw <= 128) VOB_LTC(8);
+    VOB_LTC(16);
+#undef VOB_LTC
 }
