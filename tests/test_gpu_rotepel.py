@@ -30,6 +30,8 @@ def _configs():
     ret_one = _layer("retention", heads=1, dim=16, vdim=48, decay=(0.99,), rot_dims=16, rot_base=500.0, ff=72)
     lat = _layer("latent_attention", heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40, scale=0.3, rot_dims=8, rot_base=10000.0, ff=0)
     lat_one = _layer("latent_attention", heads=1, dim=32, rot_dim=16, vdim=8, kv_rank=24, scale=0.2, rot_dims=16, rot_base=300.0, ff=112)
+    # latent and rotated sizes that are multiples of 16: in bfloat16 prompt portions take the tensor-core kernel
+    lat_16 = _layer("latent_attention", heads=5, dim=16, rot_dim=16, vdim=8, kv_rank=48, scale=0.25, rot_dims=16, rot_base=1000.0, ff=64)
     return {
         # three streams, one norm group, a loop of three passes over the first two layers
         "A": RotepelConfig(vocab=97, width=64, layers=(delta, lat, ret), norm_eps=1e-5, norm_groups=1, streams=3, loop=(0, 2, 3)),
@@ -37,6 +39,8 @@ def _configs():
         "B": RotepelConfig(vocab=131, width=96, layers=(ret_one, delta_wide, lat_one), norm_eps=1e-6, norm_groups=3, streams=None),
         # one stream with coefficients of its own, four groups, a loop that runs once, attention twice
         "C": RotepelConfig(vocab=64, width=64, layers=(lat, delta, lat_one), norm_eps=1e-5, norm_groups=4, streams=1, loop=(1, 3, 1)),
+        # attention whose sizes the tensor-core kernel takes, twice in a loop, beside retention; 42 is no multiple of 4
+        "T": RotepelConfig(vocab=77, width=42, layers=(lat_16, ret_one), norm_eps=1e-5, norm_groups=3, streams=2, loop=(0, 1, 2)),
         "delta": RotepelConfig(vocab=50, width=48, layers=(delta,), norm_eps=1e-5, norm_groups=2, streams=2),
         "retention": RotepelConfig(vocab=50, width=48, layers=(ret,), norm_eps=1e-5, norm_groups=2, streams=2),
         "latent": RotepelConfig(vocab=50, width=48, layers=(lat,), norm_eps=1e-5, norm_groups=2, streams=2),
@@ -77,6 +81,17 @@ def _tokens(n, vocab, seed):
 TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 
 
+def _close(got, want, dtype) -> bool:
+    """float32: every logit within TOL of the largest. bfloat16: the typical row tight (root mean square of a row's
+    error against that of its logits, averaged over the rows, below 2.5e-2: measured 0.6e-2 to 1.8e-2 on these models,
+    the same with either attention kernel) and no logit anywhere off by more than a tenth of the largest. A key that
+    is skipped, a wrong page or a lost state moves rows by far more than either bound."""
+    if dtype == "float32":
+        return max_rel_diff(got, want) < TOL[dtype]
+    err = (got.double() - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt()
+    return float(err.mean()) < 2.5e-2 and max_rel_diff(got, want) < 0.1
+
+
 def _poison(runner):
     """Whatever lies in pages and slots that nobody holds must never be read."""
     for ts in runner.pools.kv.values():
@@ -108,7 +123,7 @@ def _replay(session, reqs, schedule, first_step=0):
 def test_stream_norm_kernel_pending_write_groups_and_row_list():
     from vllm_oxide_b200 import kernels
     torch.manual_seed(0)
-    for S, W, groups, T in ((1, 64, 1, 5), (3, 96, 4, 7), (8, 40, 5, 3)):
+    for S, W, groups, T in ((1, 64, 1, 5), (3, 96, 4, 7), (8, 40, 5, 3), (2, 42, 3, 4)):       # the last: no 16-byte accesses
         x = torch.randn(T, S, W, device=DEV)
         y = torch.randn(T, W, device=DEV)
         mix, outc, inc, w = torch.randn(S, S, device=DEV), torch.randn(S, device=DEV), torch.randn(S, device=DEV), torch.randn(W, device=DEV)
@@ -279,13 +294,15 @@ def test_latent_attend_kernel_far_key_page_borders_and_first_tokens(dtype):
     assert torch.all(out2[7] == 0) and torch.equal(out2[8:], out[8:])
 
 
-def test_latent_attend_tensor_core_kernel_against_float64():
+@pytest.mark.parametrize("H,L,R", [(5, 48, 16), (9, 128, 32), (3, 288, 32), (2, 512, 64)])
+def test_latent_attend_tensor_core_kernel_against_float64(H, L, R):
     """Prompt portions on the tensor cores: two requests in one launch, the second with 37 keys already cached,
-    pages scattered, five heads (a block of four and a block of one), tiles of 16 tokens that end inside a
-    portion, one dominant key far back and one at the row's own position."""
+    pages scattered, head counts that leave a block partly empty, tiles of 16 tokens that end inside a portion,
+    one dominant key far back and one at the row's own position; latents of one warp per head (up to 256
+    columns) and of two (288, 512), key tiles that fit the registers fetched ahead and ones that do not."""
     from vllm_oxide_b200 import kernels
     torch.manual_seed(4)
-    H, L, R, page, scale = 5, 48, 16, 8, 0.4
+    page, scale = 8, 0.4
     lens, ctxs = (100, 50), (0, 37)
     total = [c + n for c, n in zip(ctxs, lens)]
     pages_per = [-(-t // page) for t in total]
@@ -349,7 +366,7 @@ def test_each_mixer_alone_whole_prompt_and_token_by_token(tmp_path, name, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "T"])
 def test_portions_unequal_batches_and_reuse(tmp_path, name, dtype):
     """Three requests of unequal length in a pool that cannot hold them all at once: portions from 2
     tokens up beside single tokens, a request that sits out a step, a fourth request that takes over a
@@ -367,7 +384,7 @@ def test_portions_unequal_batches_and_reuse(tmp_path, name, dtype):
     got = _replay(s, reqs, schedule)
     for k in reqs:
         assert got[k].shape[0] == len(reqs[k])
-        assert max_rel_diff(got[k], want[k]) < TOL[dtype], k
+        assert _close(got[k], want[k], dtype), k
     assert runner.manager.num_free_slots() == 3 and runner.manager.check_invariants() == ""
     if dtype == "float32":
         # each alone, whole: what a row gives does not depend on the cut or the batch
