@@ -88,11 +88,15 @@ class CachePools:
             self.kv[c] = tuple(torch.zeros((self.num_pages, t.heads, page_size, t.width), dtype=t.dtype or dtype, device=device)
                                for t in cs.paged_tensors())
         # fixed-size per-request state, one tensor per call whose mixer asks for it
-        self.state: Dict[int, torch.Tensor] = {}
+        # (a mixer that names several tensors gets a tuple of them)
+        self.state: Dict[int, object] = {}
         for idx, call in enumerate(spec.schedule):
             ss = spec.blocks[call.layer].mixer.state_spec()
-            if ss is not None:
-                self.state[idx] = torch.zeros((max_seqs,) + tuple(ss.shape), dtype=ss.dtype, device=device)
+            if ss is None:
+                continue
+            made = tuple(torch.zeros((max_seqs,) + tuple(x.shape), dtype=x.dtype, device=device)
+                         for x in (ss if isinstance(ss, (tuple, list)) else (ss,)))
+            self.state[idx] = made if isinstance(ss, (tuple, list)) else made[0]
 
     @property
     def num_groups(self) -> int:
@@ -105,8 +109,9 @@ class CachePools:
 
     def reset_slot(self, slot: int) -> None:
         """A request was admitted to this slot: its state starts from zero."""
-        for t in self.state.values():
-            t[slot].zero_()
+        for st in self.state.values():
+            for t in (st if isinstance(st, tuple) else (st,)):
+                t[slot].zero_()
 
     def bytes_per_token(self) -> int:
         return sum(self.page_bytes) // self.page_size

@@ -1,0 +1,263 @@
+// Softmax attention over a paged cache whose keys and values have sizes of their own, with the
+// options a design may switch on one by one: rotary positions on part of each head, q and k brought
+// to unit root mean square, a query factor that grows with the position, values mixed with those an
+// earlier layer made of the same token, a window, a sink in the softmax, a sigmoid gate on the result.
+//
+// Two steps per call of a layer:
+//   vob_flex_prep      per token: q, k, v (columns of one projection output) -> q' to a buffer, k' and
+//                      v' to their cache slots;
+//   vob_flex_attention per (row, head a), the row at position p of its request, g = a / (H / G):
+//       s_j = (q'_a . K[j, g]) * scale          for keys j in [first, p], first = max(0, p + 1 - window)
+//       den = sum_j exp(s_j) (+ exp(sink_a): a key with no value, counted once)
+//       out_a = sum_j exp(s_j) V[j, g] / den    (* sigmoid(gate) * out_scale)
+// The step's own keys are in the cache before they are read. Scores, softmax, angles, norms and the
+// query factor are float32. Cache layout per layer: K [pages][G][page_size][D], V [pages][G][page_size][DV].
+#include "common.cuh"
+VOB_PDL_SWITCH(attention_flex)
+
+// ---------------------------------------------------------------------------------------------
+// Preparation. One block of 128 threads per token; a warp takes one head at a time (q heads, then k
+// heads, then v heads), lane l holding features l, l + 32, ... (heads up to 256 wide).
+//   q, k:  the first `rot` features of a head are rotated, feature i with i + rot / 2, by
+//          float(pos) * inv_freq[i]; then (unit_rms) the head is divided by sqrt(mean(x^2) + eps);
+//          q is also multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0).
+//   v:     v_mode 1: the values are also left in `v_first` [T, G * DV] for later layers of this step;
+//          v_mode 2: v <- (1 - lambda) v + lambda v_first, lambda = *vmix.
+// Rows with a negative position (padding) are left alone; a negative slot skips the cache write.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const int* __restrict__ positions,
+                 const int* __restrict__ slots, const float* __restrict__ inv_freq, int rot, int unit_rms, float eps,
+                 float temp_coef, int temp_every, const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode,
+                 T* __restrict__ q_out, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D, int DV,
+                 int page_size) {
+    pdl_launch_dependents();
+    pdl_wait(61);
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int slot = slots ? slots[t] : -1;
+    const T* row = proj + (size_t)t * ld;
+    const int half = rot >> 1;
+    const float fpos = (float)pos;
+    for (int job = warp; job < H + 2 * G; job += 4) {
+        if (job < H + G) {
+            const bool is_q = job < H;
+            const int head = is_q ? job : job - H;
+            const T* src = row + (is_q ? q_off : k_off) + (size_t)head * D;
+            float x[8];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int f = lane + 32 * i;
+                float v = 0.f;
+                if (f < D) {
+                    if (f < rot) {
+                        const int idx = f < half ? f : f - half;
+                        const float ang = fpos * inv_freq[idx];
+                        const float cs = cosf(ang), sn = sinf(ang);
+                        const float a = ld_f(src + idx), b = ld_f(src + idx + half);
+                        v = f < half ? a * cs - b * sn : b * cs + a * sn;
+                    } else {
+                        v = ld_f(src + f);
+                    }
+                }
+                x[i] = v;
+                ss = fmaf(v, v, ss);
+            }
+            float mul = 1.f;
+            if (unit_rms) mul = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+            if (is_q && temp_every > 0) mul *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+            T* dst;
+            if (is_q) {
+                dst = q_out + (size_t)t * ld_q + (size_t)head * D;
+            } else {
+                if (slot < 0) continue;
+                dst = kcache + ((size_t)((slot / page_size) * G + head) * page_size + slot % page_size) * D;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int f = lane + 32 * i;
+                if (f < D) st_f(dst + f, x[i] * mul);
+            }
+        } else {
+            const int head = job - H - G;
+            const T* src = row + v_off + (size_t)head * DV;
+            T* vf = v_first ? v_first + ((size_t)t * G + head) * DV : nullptr;
+            T* dst = slot >= 0 ? vcache + ((size_t)((slot / page_size) * G + head) * page_size + slot % page_size) * DV : nullptr;
+            const float lam = v_mode == 2 ? *vmix : 0.f;
+            for (int f = lane; f < DV; f += 32) {
+                float v = ld_f(src + f);
+                if (v_mode == 2) v = (1.0f - lam) * v + lam * ld_f(vf + f);
+                if (v_mode == 1) st_f(vf + f, v);
+                if (dst) st_f(dst + f, v);
+            }
+        }
+    }
+}
+
+VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int k_off, int v_off, const int* positions,
+                             const int* slots, const float* inv_freq, int rot, int unit_rms, float eps, float temp_coef,
+                             int temp_every, const float* vmix, void* v_first, int v_mode, void* q_out, long ld_q, void* kcache,
+                             void* vcache, int T, int H, int G, int D, int DV, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || D <= 0 || DV <= 0 || page_size <= 0 || rot < 0 || rot > D || (rot & 1)) return VOB_ERR_BAD_ARG;
+    if (D > 256) return VOB_ERR_UNSUPPORTED;
+    if (rot > 0 && !inv_freq) return VOB_ERR_BAD_ARG;
+    if ((v_mode == 1 || v_mode == 2) && !v_first) return VOB_ERR_BAD_ARG;
+    if (v_mode == 2 && !vmix) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(flex_prep_kernel<ElemT>, dim3(T), dim3(128), 0, stream, (const ElemT*)proj, ld, q_off,
+                                              k_off, v_off, positions, slots, inv_freq, rot, unit_rms, eps, temp_coef, temp_every, vmix,
+                                              (ElemT*)v_first, v_mode, (ElemT*)q_out, ld_q, (ElemT*)kcache, (ElemT*)vcache, H, G, D, DV,
+                                              page_size));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// General kernel: one warp per (row, head). Keys are visited in chunks of 32: each lane scores one
+// key against q held in shared memory, the warp agrees on the running maximum, then the 32 weighted
+// value rows are summed with lane l holding value features l, l + 32, ... Any D, DV up to 256, any
+// H, G, page size. This is the kernel of the 32-bit engine and the one the bfloat16 engine falls
+// back to. A row's result depends only on its own q and keys, never on the batch around it: keys
+// are walked from the first visible one in chunks that start there.
+// Launch: ceil(T * H / 4) blocks of 128 threads; 4 * D floats of shared memory.
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    __device__ static inline void load(const float* p, float* o) {
+        float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static inline void load(const __nv_bfloat16* p, float* o) {
+        uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            o[2 * i] = f.x; o[2 * i + 1] = f.y;
+        }
+    }
+};
+
+__device__ __forceinline__ float flex_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(128, 8)
+flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out, long out_stride,
+                           const T* __restrict__ kcache, const T* __restrict__ vcache, const int* __restrict__ block_tables,
+                           int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions, int T_rows, int H,
+                           int G, int D, int DV, int page_size, int window, float scale, const float* __restrict__ sink,
+                           const T* __restrict__ gate, long gate_stride, float out_scale) {
+    pdl_launch_dependents();
+    pdl_wait(62);
+    extern __shared__ float qs_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * 4 + warp;
+    if (w >= (long long)T_rows * H) return;          // whole warp leaves together
+    const int row = (int)(w / H), head = (int)(w % H);
+    const int g = head / (H / G);
+    T* op = out + (size_t)row * out_stride + (size_t)head * DV;
+    const int pos = positions[row];
+    if (pos < 0) {                                   // a padding row: no keys, zero output
+        for (int d = lane; d < DV; d += 32) st_f(op + d, 0.f);
+        return;
+    }
+    float* qs = qs_all + warp * D;
+    const T* qp = q + (size_t)row * q_stride + (size_t)head * D;
+    for (int d = lane; d < D; d += 32) qs[d] = ld_f(qp + d);
+    __syncwarp();
+    const int seq = row_seq[row];
+    const int* bt = block_tables + (size_t)seq * max_pages;
+    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = D % VN == 0;                    // a key row then starts on a 16-byte boundary
+    float m = -INFINITY, l = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+    for (int c0 = first; c0 <= pos; c0 += 32) {
+        const int j = c0 + lane;
+        const bool valid = j <= pos;
+        int slot_row = 0;                            // row of key j in the [.., D] / [.., DV] view of the layer's cache
+        float s = -INFINITY;
+        if (valid) {
+            const int page = bt[j / page_size];
+            slot_row = (page * G + g) * page_size + (j % page_size);
+            const T* kp = kcache + (size_t)slot_row * D;
+            float dot = 0.f;
+            if (vec) {
+                for (int d = 0; d < D; d += VN) {
+                    float kv[VN];
+                    Vec16<T>::load(kp + d, kv);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) dot = fmaf(qs[d + i], kv[i], dot);
+                }
+            } else {
+                for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ld_f(kp + d), dot);
+            }
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float alpha = expf(m - m_new);         // 0 on the first chunk (m = -inf)
+        l = l * alpha + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+        m = m_new;
+        const int nk = min(32, pos - c0 + 1);
+        for (int jj = 0; jj < nk; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int sr = __shfl_sync(0xffffffffu, slot_row, jj);
+            const T* vp = vcache + (size_t)sr * DV;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int d = lane + 32 * i;
+                if (d < DV) acc[i] = fmaf(pj, ld_f(vp + d), acc[i]);
+            }
+        }
+    }
+    if (sink) {                                      // one more term in the denominator, no value
+        const float sk = sink[head];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+    }
+    const float inv_l = out_scale / l;
+    const T* gp = gate ? gate + (size_t)row * gate_stride + (size_t)head * DV : nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        if (d < DV) {
+            float v = acc[i] * inv_l;
+            if (gp) v *= flex_sigmoid(ld_f(gp + d));
+            st_f(op + d, v);
+        }
+    }
+}
+
+VOB_EXPORT int vob_flex_attention(const void* q, long q_stride, void* out, long out_stride, const void* kcache, const void* vcache,
+                                  int code, const int* block_tables, int max_pages, const int* row_seq, const int* positions,
+                                  int T_rows, int H, int G, int D, int DV, int page_size, int window, float scale,
+                                  const float* sink, const void* gate, long gate_stride, float out_scale, cudaStream_t stream) {
+    if (T_rows <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || max_pages <= 0 || D <= 0 || DV <= 0) return VOB_ERR_BAD_ARG;
+    if (D > 256 || DV > 256) return VOB_ERR_UNSUPPORTED;
+    const long long warps = (long long)T_rows * H;
+    const long long blocks = (warps + 3) / 4;
+    if (blocks > 0x7fffffffLL) return VOB_ERR_UNSUPPORTED;
+    const size_t smem = 4 * (size_t)D * sizeof(float);
+    VOB_DISPATCH_ELEM(code, return vob_launch(flex_attention_warp_kernel<ElemT>, dim3((unsigned)blocks), dim3(128), smem, stream,
+                                              (const ElemT*)q, q_stride, (ElemT*)out, out_stride, (const ElemT*)kcache,
+                                              (const ElemT*)vcache, block_tables, max_pages, row_seq, positions, T_rows, H, G, D, DV,
+                                              page_size, window, scale, sink, (const ElemT*)gate, gate_stride, out_scale));
+    return 0;
+}

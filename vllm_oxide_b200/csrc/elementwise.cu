@@ -9,14 +9,14 @@
 VOB_PDL_SWITCH(elementwise)
 
 // ---------------------------------------------------------------------------------------------
-// Embedding gather: out[t, :] = table[tokens[t], :]   (float32 out)
+// Embedding gather: out[t, :] = table[tokens[t], :] * scale   (float32 out; scale 1 leaves the row as it is)
 // Reference op: crates/engine/src/backend/cpu/mod.rs:172-180.
 // Launch: one block per token, 256 threads. Bound: memory (2 * h * 4 bytes per token).
 // A token outside [0, vocab) writes zeros and raises *err_flag (the host checks ids first).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int h, int vocab, int* err_flag) {
+                             float* __restrict__ out, int h, int vocab, int* err_flag, float scale) {
     pdl_launch_dependents();
     pdl_wait(1);
     int t = blockIdx.x;
@@ -25,14 +25,14 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     if (!ok && threadIdx.x == 0 && err_flag) atomicExch(err_flag, 1);
     const T* src = table + (size_t)(ok ? tok : 0) * h;
     float* dst = out + (size_t)t * h;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = ok ? ld_f(src + i) : 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = ok ? ld_f(src + i) * scale : 0.f;
 }
 
 VOB_EXPORT int vob_embed(const void* table, int table_code, const int* tokens, float* out, int T, int h,
-                         int vocab, int* err_flag, cudaStream_t stream) {
+                         int vocab, int* err_flag, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (h <= 0 || vocab <= 0) return VOB_ERR_BAD_ARG;
-    VOB_DISPATCH_ELEM(table_code, return vob_launch(embed_kernel<ElemT>, dim3(T), dim3(256), 0, stream, (const ElemT*)table, tokens, out, h, vocab, err_flag));
+    VOB_DISPATCH_ELEM(table_code, return vob_launch(embed_kernel<ElemT>, dim3(T), dim3(256), 0, stream, (const ElemT*)table, tokens, out, h, vocab, err_flag, scale));
     return 0;
 }
 
@@ -81,7 +81,7 @@ VOB_EXPORT int vob_embed_fold(const void* table, int table_code, const int* toke
 
 // ---------------------------------------------------------------------------------------------
 // Residual add + RMSNorm:
-//   x = resid[src] (+ delta[src]);  if no row list: resid[src] = x  (the residual sum, float32)
+//   x = resid[src] (+ delta[src] (* dscale, per feature));  if no row list: resid[src] = x  (the residual sum, float32)
 //   out[r] = w * (x * 1/sqrt(mean(x^2) + eps))
 // Reference ops: add (crates/engine/src/backend/cpu/mod.rs:351-358) followed by rmsnorm
 // (:182-197); the weight multiplies last, as there. With a row list (`rows`, R entries) only
@@ -94,7 +94,7 @@ VOB_EXPORT int vob_embed_fold(const void* table, int table_code, const int* toke
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, const int* __restrict__ rows,
-                                   TO* __restrict__ out, int h, float eps) {
+                                   TO* __restrict__ out, int h, float eps, const float* __restrict__ dscale) {
     pdl_launch_dependents();
     pdl_wait(2);
     extern __shared__ float row[];
@@ -107,7 +107,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     for (int i = threadIdx.x; i < h; i += blockDim.x) {
         float v = x[i];
         if (d) {
-            v += ld_f(d + i);
+            v += dscale ? ld_f(d + i) * dscale[i] : ld_f(d + i);
             if (!rows) x[i] = v;
         }
         row[i] = v;
@@ -162,7 +162,7 @@ template <> struct Store4<__nv_bfloat16> {
 template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
-                       const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
+                       const int* __restrict__ rows, TO* __restrict__ out, int h, float eps, const float* __restrict__ dscale) {
     pdl_launch_dependents();
     pdl_wait(2);
     __shared__ float red[32];
@@ -178,6 +178,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, 
         if (i < nvec) {
             v[k] = *reinterpret_cast<const float4*>(x + 4 * i);
             dv[k] = d ? Load4<TD>::ld(d + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (d && dscale) {
+                const float4 sc = *reinterpret_cast<const float4*>(dscale + 4 * i);
+                dv[k].x *= sc.x; dv[k].y *= sc.y; dv[k].z *= sc.z; dv[k].w *= sc.w;
+            }
             w[k] = *reinterpret_cast<const float4*>(weight + 4 * i);
         }
     }
@@ -214,31 +218,31 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta, 
 
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* resid, const void* delta, const float* weight, const int* rows, void* out, int R,
-                              int h, float eps, cudaStream_t stream) {
-    bool aligned = (h % 4 == 0) && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) % 16 == 0);
+                              int h, float eps, const float* dscale, cudaStream_t stream) {
+    bool aligned = (h % 4 == 0) && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out | (uintptr_t)dscale) % 16 == 0);
     int nv = (h / 4 + 255) / 256;
     if (aligned && nv <= 8) {
-#define VEC(NV) return vob_launch(add_rmsnorm_vec_kernel<TD, TO, NV>, dim3(R), dim3(256), 0, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps)
+#define VEC(NV) return vob_launch(add_rmsnorm_vec_kernel<TD, TO, NV>, dim3(R), dim3(256), 0, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps, dscale)
         if (nv <= 1) VEC(1); else if (nv <= 2) VEC(2); else if (nv <= 4) VEC(4); else VEC(8);
 #undef VEC
     }
     size_t smem = (size_t)h * sizeof(float);
     if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
-    return vob_launch(add_rmsnorm_kernel<TD, TO>, dim3(R), dim3(256), smem, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps);
+    return vob_launch(add_rmsnorm_kernel<TD, TO>, dim3(R), dim3(256), smem, stream, resid, (const TD*)delta, weight, rows, (TO*)out, h, eps, dscale);
 }
 
 VOB_EXPORT int vob_add_rmsnorm(float* resid, const void* delta, int delta_code, const float* weight,
                                const int* rows, void* out, int out_code, int R, int h, float eps,
-                               cudaStream_t stream) {
+                               const float* dscale, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (h <= 0) return VOB_ERR_BAD_ARG;
     if (!delta) delta_code = VOB_F32;
     if (out_code == VOB_F32) {
-        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, float>(resid, delta, weight, rows, out, R, h, eps, stream);
-        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, weight, rows, out, R, h, eps, stream);
+        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, float>(resid, delta, weight, rows, out, R, h, eps, dscale, stream);
+        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, weight, rows, out, R, h, eps, dscale, stream);
     } else if (out_code == VOB_BF16) {
-        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, stream);
-        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, stream);
+        if (delta_code == VOB_F32) return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, dscale, stream);
+        if (delta_code == VOB_BF16) return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, rows, out, R, h, eps, dscale, stream);
     }
     return VOB_ERR_BAD_ARG;
 }
@@ -508,12 +512,19 @@ VOB_EXPORT int vob_rope_kv_write(void* q, long long q_stride, void* k, long long
 }
 
 // ---------------------------------------------------------------------------------------------
-// SwiGLU: out[t, j] = gate / (1 + exp(-gate)) * up, gate = in[t, j], up = in[t, I + j]
-// (divide, then multiply by up, as crates/engine/src/backend/cpu/mod.rs:341-349). The input is
+// Gated activation: out[t, j] = act(gate) * up, gate = in[t, j], up = in[t, I + j].
+// ACT 0, SwiGLU: gate / (1 + exp(-gate)) * up
+// (divide, then multiply by up, as crates/engine/src/backend/cpu/mod.rs:341-349).
+// ACT 1, the tanh form of gelu: 0.5 gate (1 + tanh(sqrt(2/pi) (gate + 0.044715 gate^3))) * up. The input is
 // the output of one fused [gate; up] matrix product, row stride `in_stride` elements.
 // Launch: grid (T, ceil(I/256)). Bound: memory.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+template <int ACT> __device__ __forceinline__ float glu_act(float g) {
+    if (ACT == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+
+template <typename T, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
     pdl_launch_dependents();
     pdl_wait(5);
@@ -521,11 +532,11 @@ __global__ void swiglu_kernel(const T* __restrict__ in, long long in_stride, T* 
     if (j >= I) return;
     const T* r = in + (size_t)blockIdx.x * in_stride;
     float g = ld_f(r + j), u = ld_f(r + I + j);
-    st_f(out + (size_t)blockIdx.x * I + j, g / (1.0f + expf(-g)) * u);
+    st_f(out + (size_t)blockIdx.x * I + j, glu_act<ACT>(g) * u);
 }
 
 // 16 bytes per load: 8 bfloat16 or 4 float per thread (I a multiple of that, rows 16-byte aligned).
-template <typename T, int N>
+template <typename T, int N, int ACT>
 __global__ void swiglu_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I) {
     pdl_launch_dependents();
     pdl_wait(5);
@@ -541,12 +552,12 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ in, long long in_stride,
 #pragma unroll
     for (int e = 0; e < N; ++e) {
         float gf = ld_f(g + e), uf = ld_f(u + e);
-        st_f(o + e, gf / (1.0f + expf(-gf)) * uf);
+        st_f(o + e, glu_act<ACT>(gf) * uf);
     }
     *reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * I + j) = ov;
 }
 
-template <typename T>
+template <typename T, int ACT>
 static int launch_swiglu(const void* in, long long in_stride, void* out, int T_rows, int I, cudaStream_t stream) {
     constexpr int N = 16 / sizeof(T);
     bool vec = (I % N == 0) && (in_stride % N == 0) && (((uintptr_t)in | (uintptr_t)out) % 16 == 0);
@@ -554,11 +565,11 @@ static int launch_swiglu(const void* in, long long in_stride, void* out, int T_r
         int per = 256 * N;
         if ((I + per - 1) / per > 65535) return VOB_ERR_UNSUPPORTED;
         dim3 grid(T_rows, (I + per - 1) / per);
-        return vob_launch(swiglu_vec_kernel<T, N>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
+        return vob_launch(swiglu_vec_kernel<T, N, ACT>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
     } else {
         if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
         dim3 grid(T_rows, (I + 255) / 256);
-        return vob_launch(swiglu_kernel<T>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
+        return vob_launch(swiglu_kernel<T, ACT>, grid, dim3(256), 0, stream, (const T*)in, in_stride, (T*)out, I);
     }
 }
 
@@ -566,7 +577,18 @@ VOB_EXPORT int vob_swiglu(const void* in, long long in_stride, void* out, int co
                           cudaStream_t stream) {
     if (T <= 0) return 0;
     if (I <= 0) return VOB_ERR_BAD_ARG;
-    if (code == VOB_F32) return launch_swiglu<float>(in, in_stride, out, T, I, stream);
-    if (code == VOB_BF16) return launch_swiglu<__nv_bfloat16>(in, in_stride, out, T, I, stream);
+    if (code == VOB_F32) return launch_swiglu<float, 0>(in, in_stride, out, T, I, stream);
+    if (code == VOB_BF16) return launch_swiglu<__nv_bfloat16, 0>(in, in_stride, out, T, I, stream);
+    return VOB_ERR_BAD_ARG;
+}
+
+// The same with the activation chosen by `act` (0 silu, 1 the tanh form of gelu).
+VOB_EXPORT int vob_glu(const void* in, long long in_stride, void* out, int code, int T, int I, int act,
+                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (I <= 0 || (act != 0 && act != 1)) return VOB_ERR_BAD_ARG;
+    if (act == 0) return vob_swiglu(in, in_stride, out, code, T, I, stream);
+    if (code == VOB_F32) return launch_swiglu<float, 1>(in, in_stride, out, T, I, stream);
+    if (code == VOB_BF16) return launch_swiglu<__nv_bfloat16, 1>(in, in_stride, out, T, I, stream);
     return VOB_ERR_BAD_ARG;
 }

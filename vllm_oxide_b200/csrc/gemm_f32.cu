@@ -15,7 +15,7 @@ VOB_PDL_SWITCH(gemm_f32)
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
-                float* __restrict__ C, long long ldc, int M, int N, int K) {
+                float* __restrict__ C, long long ldc, int M, int N, int K, const float* __restrict__ bias) {
     pdl_launch_dependents();
     pdl_wait(11);
     __shared__ float As[TK][TM + 4];
@@ -86,16 +86,17 @@ gemm_f32_kernel(const float* __restrict__ A, long long lda, const float* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int gn = n0 + tx * 4 + j;
-            if (gn < N) C[(size_t)gm * ldc + gn] = acc[i][j];
+            if (gn < N) C[(size_t)gm * ldc + gn] = bias ? acc[i][j] + bias[gn] : acc[i][j];
         }
     }
 }
 
+// `bias` (N entries, may be null) is added to every row after the sum over k.
 VOB_EXPORT int vob_gemm_f32(const float* A, long long lda, const float* W, long long ldw, float* C,
-                            long long ldc, int M, int N, int K, cudaStream_t stream) {
+                            long long ldc, int M, int N, int K, const float* bias, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || lda < K || ldw < K || ldc < N) return VOB_ERR_BAD_ARG;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return VOB_ERR_UNSUPPORTED;
-    return vob_launch(gemm_f32_kernel, grid, dim3(256), 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
+    return vob_launch(gemm_f32_kernel, grid, dim3(256), 0, stream, A, lda, W, ldw, C, ldc, M, N, K, bias);
 }

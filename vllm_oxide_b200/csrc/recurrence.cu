@@ -3,9 +3,11 @@
 // token, across steps:
 //     mode 0 (delta rule with decay):  S_t = diag(w_t) S_(t-1) - b_t (u_t^T S_(t-1)) + k_t v_t^T
 //     mode 1 (fixed decay per head):   S_t = d_h S_(t-1) + k_t v_t^T
+//     mode 2 (gated delta rule):       S' = diag(w_t) S_(t-1);  S_t = S' + k_t (b_t (v_t - S'^T k_t))^T
 //     o_t = S_t^T r_t
 // w_t, b_t, u_t are float32 vectors per token, head and key channel, prepared by vob_delta_prep (or
-// by anything else that writes them); d_h is one number per head.
+// by anything else that writes them); d_h is one number per head; in mode 2 b_t is one number per token
+// and head (the writing strength) and several heads may share one r and k (`rk_div` heads each).
 //
 // Every value column of S evolves on its own, so the work is cut by columns: a block owns VT
 // columns of one head of one request, KS threads share a column (thread q of them holds key
@@ -16,6 +18,8 @@
 // of a token never depends on how the tokens were cut into steps or what else is in the batch.
 //
 // Beside the scan: vob_delta_prep (unit key, removal rate, decay from its low-rank projection),
+// vob_gated_delta_prep (short causal convolutions with silu, unit q and k, writing strength, decay from
+// softplus) with vob_conv_state_update (the convolutions' last inputs, kept per request),
 // vob_rotate_scale (rotary positions on the first `rot` features of every head, times a scale,
 // to float32) and vob_recurrence_post (per-head RMS norm of o, an optional weight, a gate).
 #include "common.cuh"
@@ -110,6 +114,134 @@ VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, in
 }
 
 // ---------------------------------------------------------------------------------------------
+// Gated-delta preparation, per token. The columns x_off .. x_off + C - 1 of `proj` [T, ld] hold the q, k and v
+// projections side by side (G heads of K, G heads of K, H heads of V; C = 2 G K + H V). Each channel c passes
+// a causal convolution over the request's tokens and silu:
+//   y_t[c] = sum_i cw[c][taps - 1 - i] * x_(t - i)[c],  i = 0 .. taps - 1;   x before the step's first row comes from
+//   the request's convolution state [slots, taps - 1, C] (the last taps - 1 inputs, oldest first; zeros at the start)
+// then, all float32:
+//   q = silu(y_q) / sqrt(sum_head(.^2) + 1e-6) * K^-1/2,   k = silu(y_k) / sqrt(sum_head(.^2) + 1e-6)
+//   v = silu(y_v) (in the activations' type)
+//   strength[h] = sigmoid(proj[b_off + h])
+//   decay[h, c] = exp(-exp(a_log[h]) * softplus(low[a_off + h K + c] + dt_bias[h K + c]))
+// `low` [T, ld_low] is the output of the second, low-rank projections. Rows with a negative position
+// (padding) are skipped. Launch: one block of 128 threads per token; a warp takes one head (or one
+// head's decays, or the strengths) at a time. K up to 512.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_off, const T* __restrict__ low, long ld_low, int a_off,
+                        const float* __restrict__ cw, int taps, const float* __restrict__ cstate, const float* __restrict__ a_log,
+                        const float* __restrict__ dt_bias, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                        const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int H, int G, int K, int V,
+                        float* __restrict__ q_out, float* __restrict__ k_out, T* __restrict__ v_out, float* __restrict__ decay,
+                        float* __restrict__ strength) {
+    pdl_launch_dependents();
+    pdl_wait(45);
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (positions[t] < 0) return;
+    const int s = row_seq[t];
+    const int j = t - seq_starts[s];                 // the row's place among the request's rows of this step
+    const int C = 2 * G * K + H * V;
+    const float* st = cstate + (size_t)state_slots[s] * (taps - 1) * C;
+    auto conv_silu = [&](int c) -> float {
+        float y = 0.f;
+        for (int i = taps - 1; i >= 0; --i) {        // oldest input first
+            const int jj = j - i;
+            const float x = jj >= 0 ? ld_f(proj + (size_t)(t - i) * ld + x_off + c) : st[(size_t)(taps - 1 + jj) * C + c];
+            y = fmaf(cw[(size_t)c * taps + (taps - 1 - i)], x, y);
+        }
+        return y / (1.0f + expf(-y));
+    };
+    const int jobs = 2 * G + 2 * H + 1;
+    for (int job = warp; job < jobs; job += 4) {
+        if (job < 2 * G) {                           // a q or k head: convolution, silu, unit length
+            const bool is_q = job < G;
+            const int head = is_q ? job : job - G;
+            const int c0 = job * K;                  // q heads then k heads lie side by side
+            float x[16];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int f = lane + 32 * i;
+                x[i] = f < K ? conv_silu(c0 + f) : 0.f;
+                ss = fmaf(x[i], x[i], ss);
+            }
+            float mul = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+            if (is_q) mul *= 1.0f / sqrtf((float)K);
+            float* dst = (is_q ? q_out : k_out) + (size_t)t * G * K + (size_t)head * K;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int f = lane + 32 * i;
+                if (f < K) dst[f] = x[i] * mul;
+            }
+        } else if (job < 2 * G + H) {                // a v head: convolution, silu
+            const int head = job - 2 * G;
+            for (int f = lane; f < V; f += 32)
+                st_f(v_out + (size_t)t * H * V + (size_t)head * V + f, conv_silu(2 * G * K + head * V + f));
+        } else if (job < 2 * G + 2 * H) {            // a head's decays
+            const int head = job - 2 * G - H;
+            const float rate = expf(a_log[head]);
+            for (int f = lane; f < K; f += 32) {
+                const int ch = head * K + f;
+                const float z = ld_f(low + (size_t)t * ld_low + a_off + ch) + dt_bias[ch];
+                const float sp = z > 20.f ? z : log1pf(expf(z));
+                decay[(size_t)t * H * K + ch] = expf(-rate * sp);
+            }
+        } else {                                     // writing strengths
+            for (int h = lane; h < H; h += 32)
+                strength[(size_t)t * H + h] = sigmoidf_(ld_f(proj + (size_t)t * ld + b_off + h));
+        }
+    }
+}
+
+VOB_EXPORT int vob_gated_delta_prep(const void* proj, int code, long ld, int x_off, int b_off, const void* low, long ld_low, int a_off,
+                                    const float* cw, int taps, const float* cstate, const float* a_log, const float* dt_bias,
+                                    const int* positions, const int* row_seq, const int* seq_starts, const int* state_slots, int T,
+                                    int H, int G, int K, int V, float* q_out, float* k_out, void* v_out, float* decay,
+                                    float* strength, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || K <= 0 || V <= 0 || taps < 1 || H % G != 0) return VOB_ERR_BAD_ARG;
+    if (K > 512) return VOB_ERR_UNSUPPORTED;
+    VOB_DISPATCH_ELEM(code, return vob_launch(gated_delta_prep_kernel<ElemT>, dim3(T), dim3(128), 0, stream, (const ElemT*)proj, ld, x_off,
+                                              b_off, (const ElemT*)low, ld_low, a_off, cw, taps, cstate, a_log, dt_bias, positions, row_seq,
+                                              seq_starts, state_slots, H, G, K, V, q_out, k_out, (ElemT*)v_out, decay, strength));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The convolution state after a step: per request the last taps - 1 inputs of every channel, oldest
+// first. A request that brought n rows keeps its own last entries where n < taps - 1:
+//   new[m] = x_(n - (taps - 1) + m) if that row is of this step, else old[m + n],   m = 0 .. taps - 2
+// (in place, m ascending: old[m + n] lies behind what has been written). Runs behind the kernel
+// that read the old state. Launch: grid (requests, ceil(C / 128)).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_state_update_kernel(const T* __restrict__ proj, long ld, int x_off, int C, int taps, float* __restrict__ cstate,
+                         const int* __restrict__ seq_starts, const int* __restrict__ state_slots) {
+    pdl_launch_dependents();
+    pdl_wait(46);
+    const int s = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+    const int r0 = seq_starts[s], n = seq_starts[s + 1] - r0;
+    if (n <= 0 || c >= C) return;
+    float* st = cstate + (size_t)state_slots[s] * (taps - 1) * C;
+    for (int m = 0; m < taps - 1; ++m) {
+        const int tau = n - (taps - 1) + m;
+        st[(size_t)m * C + c] = tau >= 0 ? ld_f(proj + (size_t)(r0 + tau) * ld + x_off + c) : st[(size_t)(m + n) * C + c];
+    }
+}
+
+VOB_EXPORT int vob_conv_state_update(const void* proj, int code, long ld, int x_off, int C, int taps, float* cstate,
+                                     const int* seq_starts, const int* state_slots, int seqs, cudaStream_t stream) {
+    if (seqs <= 0 || taps <= 1) return 0;
+    if (C <= 0 || seqs > 0x7fffffff || (C + 127) / 128 > 65535) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(conv_state_update_kernel<ElemT>, dim3(seqs, (C + 127) / 128), dim3(128), 0, stream,
+                                              (const ElemT*)proj, ld, x_off, C, taps, cstate, seq_starts, state_slots));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Rotary positions and a scale, to float32: for every head of D features, feature i < rot / 2 is
 // paired with feature i + rot / 2 and the pair (a, b) becomes (a cos - b sin, b cos + a sin) with
 // the angle float(position) * inv_freq[i]; features from `rot` on pass unchanged; everything is
@@ -168,24 +300,26 @@ __global__ void __launch_bounds__(128, 1)
 recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restrict__ k, long ld_k, const TV* __restrict__ v,
                        long ld_v, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ u,
                        float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
-                       float* __restrict__ o, int H, int K, int V) {
+                       float* __restrict__ o, int H, int K, int V, int rk_div) {
     // Every size of the tiling is a constant, so that staging a token is a few plain loads and stores: what one token
     // needs is one list of PER elements (r, k and in mode 0 w, b, u over KPAD channels, then v over VT columns), thread
     // t takes elements t, t + 128, ... of it (NPT per token), and the list of the next CT tokens is fetched into
     // registers while the staged tokens are worked on. The chain from token to token is what bounds a long portion.
-    constexpr int KPAD = KS * KPT, VT = 128 / KS, NA = MODE == 0 ? 5 : 2;
+    constexpr int KPAD = KS * KPT, VT = 128 / KS, NA = MODE == 0 ? 5 : MODE == 2 ? 3 : 2;
+    constexpr int NB = MODE == 2 ? 1 : 0;          // mode 2: one more element per token, the writing strength
     // Lane q of a column holds key channels q * KPT .. q * KPT + KPT - 1. In shared memory a lane's channels lie
     // together (read four at a time), each lane's group padded by four floats so that the KS groups fall into
     // different banks: channel c of an array at (c / KPT) * (KPT + 4) + c % KPT.
     constexpr int GRP = KPT + 4, KPADP = KS * GRP;
-    constexpr int PER = NA * KPADP + VT, NPT = (NA * KPAD + VT + 127) / 128;
+    constexpr int PER = NA * KPADP + VT + 4 * NB, NPT = (NA * KPAD + VT + NB + 127) / 128;
     constexpr int CT = NPT >= 24 ? 1 : (24 / NPT > 8 ? 8 : 24 / NPT);
     pdl_launch_dependents();
     pdl_wait(43);
     const int s = blockIdx.z, h = blockIdx.y;
+    const int hk = h / rk_div;                       // the head whose r and k this head reads
     const int r0 = seq_starts[s], r1 = seq_starts[s + 1];
     if (r1 <= r0) return;
-    __shared__ __align__(16) float sm[CT * PER];     // token tt: [r | k | (w | b | u) | v] at sm + tt * PER
+    __shared__ __align__(16) float sm[CT * PER];     // token tt: [r | k | (w | b | u) | v | (strength)] at sm + tt * PER
     const int tid = threadIdx.x;
     const int q = tid % KS, jj = tid / KS;
     const int j = blockIdx.x * VT + jj;
@@ -207,14 +341,16 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
             for (int i = 0; i < NPT; ++i) {
                 const int x = tid + i * 128;            // which array and channel x is does not depend on the token
                 unsigned val = 0u;                      // the bits of 0 in either type
-                if (tt < n && x < NA * KPAD + VT) {
+                if (tt < n && x < NA * KPAD + VT + NB) {
                     if (x < NA * KPAD) {
                         const int a = x / KPAD, c = x % KPAD;
                         if (c < K) {
                             const size_t g = row * H * K + h * K + c;
-                            val = a == 0 ? raw_ld(r + row * ld_r + h * K + c) : a == 1 ? raw_ld(k + row * ld_k + h * K + c)
+                            val = a == 0 ? raw_ld(r + row * ld_r + hk * K + c) : a == 1 ? raw_ld(k + row * ld_k + hk * K + c)
                                 : a == 2 ? raw_ld(w + g) : a == 3 ? raw_ld(b + g) : raw_ld(u + g);
                         }
+                    } else if (x == NA * KPAD + VT) {
+                        val = raw_ld(b + row * H + h);
                     } else {
                         const int jv = blockIdx.x * VT + (x - NA * KPAD);
                         if (jv < V) val = raw_ld(v + row * ld_v + h * V + jv);
@@ -239,6 +375,8 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                         a < 2 ? raw_to_float<TRK>(pre[tt * NPT + i]) : __uint_as_float(pre[tt * NPT + i]);
                 } else if (x < NA * KPAD + VT) {
                     sm[tt * PER + NA * KPADP + (x - NA * KPAD)] = raw_to_float<TV>(pre[tt * NPT + i]);
+                } else if (NB && x == NA * KPAD + VT) {
+                    sm[tt * PER + NA * KPADP + VT] = __uint_as_float(pre[tt * NPT + i]);
                 }
             }
         __syncthreads();
@@ -279,6 +417,26 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                     S[4 * i + 2] = fmaf(kk[4 * i + 2], vj, fmaf(ww.z, S[4 * i + 2], -(bb.z * dot)));
                     S[4 * i + 3] = fmaf(kk[4 * i + 3], vj, fmaf(ww.w, S[4 * i + 3], -(bb.w * dot)));
                 }
+            } else if (MODE == 2) {
+                // decay first, then the delta-rule write against the decayed state, in this order
+                const float4* pw = reinterpret_cast<const float4*>(sm + tt * PER + 2 * KPADP + q * GRP);
+                const float strength = sm[tt * PER + NA * KPADP + VT];
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT / 4; ++i) {
+                    const float4 ww = pw[i];
+                    S[4 * i] *= ww.x; S[4 * i + 1] *= ww.y; S[4 * i + 2] *= ww.z; S[4 * i + 3] *= ww.w;
+                    d0 = fmaf(kk[4 * i], S[4 * i], d0);
+                    d1 = fmaf(kk[4 * i + 1], S[4 * i + 1], d1);
+                    d2 = fmaf(kk[4 * i + 2], S[4 * i + 2], d2);
+                    d3 = fmaf(kk[4 * i + 3], S[4 * i + 3], d3);
+                }
+                float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+                for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                const float uu = strength * (vj - dot);
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], uu, S[i]);
             } else {
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], vj, decay * S[i]);
@@ -309,11 +467,11 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
 template <int MODE, typename TRK, typename TV>
 static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const void* v, long ld_v, const float* w, const float* b,
                        const float* u, float* state, const int* seq_starts, const int* state_slots, float* o, int seqs, int H, int K,
-                       int V, cudaStream_t stream) {
+                       int V, int rk_div, cudaStream_t stream) {
 #define VOB_SCAN(P, KS_)                                                                                                        \
     return vob_launch(recurrence_scan_kernel<MODE, P, KS_, TRK, TV>, dim3((V + 128 / KS_ - 1) / (128 / KS_), H, seqs), dim3(128), 0,  \
                       stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, \
-                      H, K, V)
+                      H, K, V, rk_div)
     if (K <= 32) VOB_SCAN(8, 4);
     if (K <= 64) VOB_SCAN(16, 4);
     if (K <= 128) VOB_SCAN(16, 8);
@@ -324,17 +482,21 @@ static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const
 
 VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const void* k, long ld_k, int rk_code, const void* v, long ld_v,
                                    int v_code, const float* w, const float* b, const float* u, float* state, const int* seq_starts,
-                                   const int* state_slots, float* o, int seqs, int H, int K, int V, cudaStream_t stream) {
+                                   const int* state_slots, float* o, int seqs, int H, int K, int V, int rk_div, cudaStream_t stream) {
     if (seqs <= 0) return 0;
     if (H <= 0 || K <= 0 || V <= 0 || H > 65535 || seqs > 65535) return VOB_ERR_BAD_ARG;
     if (K > 512) return VOB_ERR_UNSUPPORTED;
     if (mode == 0 && (!w || !b || !u)) return VOB_ERR_BAD_ARG;
     if (mode == 1 && !w) return VOB_ERR_BAD_ARG;
-#define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, stream
+    if (mode == 2 && (!w || !b)) return VOB_ERR_BAD_ARG;
+    if (rk_div <= 0 || H % rk_div != 0 || (mode != 2 && rk_div != 1)) return VOB_ERR_BAD_ARG;
+#define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, rk_div, stream
     if (mode == 0 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<0, float, float>(VOB_ARGS);
     if (mode == 0 && rk_code == VOB_BF16 && v_code == VOB_BF16) return scan_launch<0, __nv_bfloat16, __nv_bfloat16>(VOB_ARGS);
     if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<1, float, float>(VOB_ARGS);
     if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_BF16) return scan_launch<1, float, __nv_bfloat16>(VOB_ARGS);
+    if (mode == 2 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<2, float, float>(VOB_ARGS);
+    if (mode == 2 && rk_code == VOB_F32 && v_code == VOB_BF16) return scan_launch<2, float, __nv_bfloat16>(VOB_ARGS);
 #undef VOB_ARGS
     return VOB_ERR_BAD_ARG;
 }
@@ -342,13 +504,14 @@ VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const voi
 // ---------------------------------------------------------------------------------------------
 // After the scan, per token and head: out = o / sqrt(mean(o^2) + eps) * weight * gate(g), with
 // weight optional ([H * V] float32) and gate = sigmoid (0) or silu (1) of the gate projection g, a
-// column range of a projection output [T, ld_g]. out [T, H * V] in the activations' type.
+// column range of a projection output [T, ld_g]. out [T, H * V] in the activations' type, rows `ld_out`
+// apart, everything times `out_scale`.
 // Launch: one block of 128 threads per (token, head).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
 recurrence_post_kernel(const float* __restrict__ o, const T* __restrict__ g, long ld_g, const float* __restrict__ weight,
-                       int gate_mode, float eps, int H, int V, T* __restrict__ out) {
+                       int gate_mode, float eps, int H, int V, T* __restrict__ out, long ld_out, float out_scale) {
     pdl_launch_dependents();
     pdl_wait(44);
     __shared__ float red[4];
@@ -366,15 +529,15 @@ recurrence_post_kernel(const float* __restrict__ o, const T* __restrict__ g, lon
         float val = orow[c] * inv;
         if (weight) val *= weight[h * V + c];
         val *= gate_mode == 1 ? gv * sg : sg;
-        st_f(out + (size_t)t * H * V + h * V + c, val);
+        st_f(out + (size_t)t * ld_out + h * V + c, val * out_scale);
     }
 }
 
 VOB_EXPORT int vob_recurrence_post(const float* o, const void* g, int code, long ld_g, const float* weight, int gate_mode, float eps,
-                                   int T, int H, int V, void* out, cudaStream_t stream) {
+                                   int T, int H, int V, void* out, long ld_out, float out_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || V <= 0 || H > 65535 || (gate_mode != 0 && gate_mode != 1)) return VOB_ERR_BAD_ARG;
+    if (H <= 0 || V <= 0 || H > 65535 || (gate_mode != 0 && gate_mode != 1) || ld_out < (long)H * V) return VOB_ERR_BAD_ARG;
     VOB_DISPATCH_ELEM(code, return vob_launch(recurrence_post_kernel<ElemT>, dim3(T, H), dim3(128), 0, stream, o, (const ElemT*)g, ld_g,
-                                              weight, gate_mode, eps, H, V, (ElemT*)out));
+                                              weight, gate_mode, eps, H, V, (ElemT*)out, ld_out, out_scale));
     return 0;
 }

@@ -173,6 +173,7 @@ class ModelRunner:
         self.step_graph_replays = 0
         self._folded = None
         self.after_block = None                 # debugging: a function (call number, residual, pending) run behind every block
+        self._pending_scale = None
         self._graph_launches = {}
         self._graph_pool = None
 
@@ -200,7 +201,9 @@ class ModelRunner:
         head = aligned(n * V * 4) + self.spec.final_norm.workspace_bytes(n, es)
         # an embedding may use scratch of its own beside the residual (gone before the first block runs)
         embed = getattr(self.spec.embedding, "scratch_bytes", lambda r: 0)(rows)
-        total = resid + max(embed, pending + max(block, head))
+        shared = sum(aligned(rows * cols * (es if dt is None else torch.empty((), dtype=dt).element_size()))
+                     for cols, dt in self.spec.step_buffers.values())
+        total = resid + max(embed, shared + pending + max(block, head))
         if self._can_fold(1):
             # steps of few rows run in folded form (FoldedState): residual, the next norm's input, the
             # partial sums of squares, and the blocks' folded scratch or the head
@@ -301,7 +304,8 @@ class ModelRunner:
             from ..parts.rmsnorm import RMSNorm
             self._foldable = bool(
                 self.dtype == torch.bfloat16 and self.engine.fold_norms and spec.schedule
-                and hasattr(spec.embedding, "forward_folded") and isinstance(spec.final_norm, RMSNorm)
+                and hasattr(spec.embedding, "forward_folded") and getattr(spec.embedding, "scale", 1.0) == 1.0
+                and isinstance(spec.final_norm, RMSNorm)
                 and all(getattr(spec.blocks[c.layer], "can_fold", lambda: False)() and c.cache is not None and c.write
                         for c in spec.schedule))
         return self._foldable and rows <= TUNING.few_rows
@@ -324,14 +328,21 @@ class ModelRunner:
             self._folded = self._forward_folded(ctx)
             return self._folded.resid, None
         resid = spec.embedding.forward(ctx)
+        for name, (cols, dt) in spec.step_buffers.items():
+            ctx.shared[name] = ctx.alloc((ctx.rows, cols), dt)
         es_shape = (ctx.rows, spec.hidden_size)
         pend = [ctx.alloc(es_shape), ctx.alloc(es_shape)]
         pending = None
+        self._pending_scale = None              # the per-feature scale the pending output is added with (a block may have one)
         for i, call in enumerate(spec.schedule):
             block = spec.blocks[call.layer]
             cache = self.pools.layer_cache(call.cache, call.write)
             state = self.pools.state.get(i)
-            pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1])
+            if self._pending_scale is not None:
+                pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1], pending_scale=self._pending_scale)
+            else:
+                pending = block.forward(resid, pending, ctx, cache, state, pend[i & 1])
+            self._pending_scale = getattr(block, "pending_scale", None)
             if self.after_block is not None:
                 self.after_block(i, resid, pending)
         return resid, pending
@@ -366,7 +377,10 @@ class ModelRunner:
                     # every row is wanted, in order: the head reads the folded residual directly
                     spec.lm_head.forward_folded(self._folded, spec.final_norm.eps, n, logits)
                 else:
-                    normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n)
+                    if pending is not None and getattr(self, "_pending_scale", None) is not None:
+                        normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n, delta_scale=self._pending_scale)
+                    else:
+                        normed = spec.final_norm.forward(resid, pending, ctx, rows=rows, num_rows=n)
                     spec.lm_head.forward(normed, logits)
                 temp = d[L["temperature"] + c0:L["temperature"] + c0 + n].view(torch.float32)
                 seeds = d[L["seeds"] + 2 * c0:L["seeds"] + 2 * (c0 + n)]

@@ -91,7 +91,7 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 _fn_cache = {}
 _MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling",
-            "streams", "recurrence", "latent_attention")
+            "streams", "recurrence", "latent_attention", "attention_flex")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -201,8 +201,9 @@ def set_pdl(on: bool) -> None:
 
 # ------------------------------------------------------------------------------------ embedding
 @_timed
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None) -> None:
-    """out[t] = table[tokens[t]] as float32; `tokens` int32 [T], `out` float32 [T, h]."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> None:
+    """out[t] = table[tokens[t]] * scale as float32; `tokens` int32 [T], `out` float32 [T, h]."""
     op = "embed"
     _cuda(op, table, tokens, out, err_flag)
     T = out.shape[0]
@@ -211,19 +212,19 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag
     _int32_vec(tokens, T, op, "tokens")
     if out.dtype != torch.float32 or out.dim() != 2 or out.shape[1] != table.shape[1] or not out.is_contiguous():
         raise ShapeError(op, f"out must be contiguous float32 [T, {table.shape[1]}], got {out.dtype} {list(out.shape)}")
-    f = _fn("elementwise", "vob_embed", [_P, _I, _P, _P, _I, _I, _I, _P, _P])
+    f = _fn("elementwise", "vob_embed", [_P, _I, _P, _P, _I, _I, _I, _P, _F, _P])
     _check(f(_ptr(table), _code(table, op), _ptr(tokens), _ptr(out), T, table.shape[1], table.shape[0],
-             _ptr(err_flag), _stream()), op)
+             _ptr(err_flag), float(scale), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ norm
 @_timed
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """resid (+= delta); out = weight * (x / sqrt(mean(x^2) + eps)). With `rows` (int32 [R]) only
-    those rows are normalised into out [R, h] and resid is left as it is."""
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta_scale: Optional[torch.Tensor] = None) -> None:
+    """resid (+= delta, times `delta_scale` per feature if given); out = weight * (x / sqrt(mean(x^2) + eps)).
+    With `rows` (int32 [R]) only those rows are normalised into out [R, h] and resid is left as it is."""
     op = "add_rmsnorm"
-    _cuda(op, resid, delta, weight, out, rows)
+    _cuda(op, resid, delta, weight, out, rows, delta_scale)
     if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous():
         raise ShapeError(op, f"the residual must be contiguous float32 [T, h], got {resid.dtype} {list(resid.shape)}")
     T, h = resid.shape
@@ -239,9 +240,12 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise ShapeError(op, f"out must be contiguous [>={R}, {h}], got {list(out.shape)}")
     if h * 4 > 48 * 1024:
         raise ShapeError(op, f"width {h} is beyond this kernel's limit of {48 * 1024 // 4}")
-    f = _fn("elementwise", "vob_add_rmsnorm", [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P])
+    if delta_scale is not None and (delta is None or delta_scale.dtype != torch.float32 or delta_scale.shape != (h,)
+                                    or not delta_scale.is_contiguous()):
+        raise ShapeError(op, f"delta_scale must be float32 [{h}] and come with a delta, got {delta_scale.dtype} {list(delta_scale.shape)}")
+    f = _fn("elementwise", "vob_add_rmsnorm", [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, _P])
     _check(f(_ptr(resid), _ptr(delta), _code(delta, op) if delta is not None else 0, _ptr(weight), _ptr(rows),
-             _ptr(out), _code(out, op), R, h, float(eps), _stream()), op)
+             _ptr(out), _code(out, op), R, h, float(eps), _ptr(delta_scale), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ rope + cache write
@@ -306,12 +310,32 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out, op), T, two_i // 2, _stream()), op)
 
 
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+@_timed
+def glu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[t, j] = act(gate_up[t, j]) * gate_up[t, I + j]; act is "silu" or "gelu_tanh" (the tanh form of gelu)."""
+    op = "glu"
+    _cuda(op, gate_up, out)
+    _rows_2d(gate_up, op, "gate_up")
+    T, two_i = gate_up.shape
+    if activation not in GLU_ACTIVATIONS:
+        raise ShapeError(op, f"activation {activation!r} is not known ({', '.join(GLU_ACTIVATIONS)})")
+    if two_i % 2 != 0:
+        raise ShapeError(op, f"gate_up has an odd number of columns: {two_i}")
+    if out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous {gate_up.dtype} [{T}, {two_i // 2}], got {out.dtype} {list(out.shape)}")
+    f = _fn("elementwise", "vob_glu", [_P, _L, _P, _I, _I, _I, _I, _P])
+    _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out, op), T, two_i // 2, GLU_ACTIVATIONS[activation], _stream()), op)
+
+
 # ------------------------------------------------------------------------------------ matrix products
 @_timed
-def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA chains in k order; no tensor cores)."""
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias[N]) in true float32 (FMA chains in k order; no tensor cores)."""
     op = "gemm_f32"
-    _cuda(op, a, w, out)
+    _cuda(op, a, w, out, bias)
     for name, t in (("a", a), ("w", w), ("out", out)):
         _rows_2d(t, op, name)
         if t.dtype != torch.float32:
@@ -322,8 +346,10 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise ShapeError(op, f"a has {K} columns, w has {w.shape[1]}")
     if out.shape != (M, N):
         raise ShapeError(op, f"out must be [{M}, {N}], got {list(out.shape)}")
-    f = _fn("gemm_f32", "vob_gemm_f32", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P])
-    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()), op)
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (N,) or not bias.is_contiguous()):
+        raise ShapeError(op, f"bias must be contiguous float32 [{N}], got {bias.dtype} {list(bias.shape)}")
+    f = _fn("gemm_f32", "vob_gemm_f32", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _ptr(bias), _stream()), op)
 
 
 class _GemmScratch:
@@ -659,32 +685,39 @@ def gemm_sm100_check() -> None:
                               "18-21 softmax rows); its result is not valid")
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = a @ w^T. float32 operands: the true 32-bit kernel. bfloat16 operands: this package's
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """out = a @ w^T (+ bias, a vector of the operands' type: added to the float32 sum before the result is
+    rounded; with a bias the bfloat16 product is the library's, whose epilogue adds it). float32 operands: the true 32-bit kernel. bfloat16 operands: this package's
     tcgen05 kernel (TMA operands, float32 accumulation in tensor memory); for many rows, or
     operands TMA cannot address (K not a multiple of 8, unaligned rows), the library product
     (cuBLAS through torch, float32 accumulation; above `TUNING.few_rows` rows), as the reference plans for its own matrix
     products (CLAUDE.md:107). `out` may be bfloat16 or float32."""
     op = "linear"
     if a.dtype == torch.float32:
-        gemm_f32(a, w, out)
+        gemm_f32(a, w, out, bias)
         return
-    _cuda(op, a, w, out)
+    _cuda(op, a, w, out, bias)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ShapeError(op, f"operands must both be float32 or both bfloat16, got {a.dtype} and {w.dtype}")
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or out.shape != (a.shape[0], w.shape[0]):
         raise ShapeError(op, f"shapes do not fit: a {list(a.shape)}, w {list(w.shape)}, out {list(out.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise ShapeError(op, f"out must be bfloat16 or float32, got {out.dtype}")
-    if a.shape[0] <= TUNING.few_rows and gemm_sm100_supported(a, w):
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or bias.shape != (w.shape[0],) or out.dtype != torch.bfloat16:
+            raise ShapeError(op, f"a bias must be bfloat16 [{w.shape[0]}] with a bfloat16 result, got {bias.dtype} {list(bias.shape)}")
+        _library_gemm_bf16(a, w, out, bias)
+    elif a.shape[0] <= TUNING.few_rows and gemm_sm100_supported(a, w):
         gemm_sm100(a, w, out)
     else:
         _library_gemm_bf16(a, w, out)
 
 
 @_timed
-def _library_gemm_bf16(a, w, out):
-    if out.dtype == torch.bfloat16:
+def _library_gemm_bf16(a, w, out, bias=None):
+    if bias is not None:
+        torch.addmm(bias, a, w.t(), out=out)
+    elif out.dtype == torch.bfloat16:
         torch.mm(a, w.t(), out=out)
     else:
         torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
@@ -789,10 +822,13 @@ def rotate_scale(src: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Ten
 @_timed
 def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
                     u: Optional[torch.Tensor], state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor,
-                    num_seqs: int, heads: int, out: torch.Tensor) -> None:
+                    num_seqs: int, heads: int, out: torch.Tensor, rk_heads: Optional[int] = None) -> None:
     """The recurrence over each request's rows of this step, from and to its state slot.
     mode 0: S = diag(w_t) S - b_t (u_t^T S) + k_t v_t^T with w, b, u float32 [T, heads * K];
-    mode 1: S = w[h] S + k_t v_t^T with w float32 [heads]. o_t = S^T r_t -> out float32 [T, heads * V].
+    mode 1: S = w[h] S + k_t v_t^T with w float32 [heads];
+    mode 2: S' = diag(w_t) S; S = S' + k_t (b_t (v_t - S'^T k_t))^T with w float32 [T, heads * K], b float32
+    [T, heads], and r, k float32 [T, rk_heads * K] (head h reads r and k of head h // (heads / rk_heads)).
+    o_t = S^T r_t -> out float32 [T, heads * V].
     state float32 [slots, heads, K, V]; r, k [T, heads * K] and v [T, heads * V] with any row stride."""
     op = "recurrence_scan"
     _cuda(op, r, k, v, w, b, u, state, seq_starts, state_slots, out)
@@ -802,8 +838,11 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         raise ShapeError(op, f"state must be contiguous float32 [slots, {heads}, K, V], got {state.dtype} {list(state.shape)}")
     K, V = state.shape[2], state.shape[3]
     T = r.shape[0]
-    if r.shape != (T, heads * K) or k.shape != (T, heads * K) or v.shape != (T, heads * V) or r.dtype != k.dtype:
-        raise ShapeError(op, f"r, k [{T}, {heads * K}] and v [{T}, {heads * V}] are needed, got {list(r.shape)}, {list(k.shape)}, {list(v.shape)}")
+    rk_heads = heads if rk_heads is None else int(rk_heads)
+    if rk_heads <= 0 or heads % rk_heads != 0 or (mode != 2 and rk_heads != heads):
+        raise ShapeError(op, f"{heads} heads cannot share the r and k of {rk_heads} heads in mode {mode}")
+    if r.shape != (T, rk_heads * K) or k.shape != (T, rk_heads * K) or v.shape != (T, heads * V) or r.dtype != k.dtype:
+        raise ShapeError(op, f"r, k [{T}, {rk_heads * K}] and v [{T}, {heads * V}] are needed, got {list(r.shape)}, {list(k.shape)}, {list(v.shape)}")
     if out.shape != (T, heads * V) or out.dtype != torch.float32 or not out.is_contiguous():
         raise ShapeError(op, f"out must be contiguous float32 [{T}, {heads * V}], got {out.dtype} {list(out.shape)}")
     if mode == 0:
@@ -812,34 +851,110 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                 raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {heads * K}]")
     elif mode == 1:
         _f32_vec(w, heads, op, "w")
+    elif mode == 2:
+        if r.dtype != torch.float32:
+            raise ShapeError(op, f"mode 2 takes float32 r and k, got {r.dtype}")
+        if w is None or w.dtype != torch.float32 or w.shape != (T, heads * K) or not w.is_contiguous():
+            raise ShapeError(op, f"w must be contiguous float32 [{T}, {heads * K}]")
+        if b is None or b.dtype != torch.float32 or b.shape != (T, heads) or not b.is_contiguous():
+            raise ShapeError(op, f"b must be contiguous float32 [{T}, {heads}]")
     else:
         raise ShapeError(op, f"mode {mode} is not known")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(state_slots, num_seqs, op, "state_slots")
-    f = _fn("recurrence", "vob_recurrence_scan", [_I, _P, _L, _P, _L, _I, _P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P])
+    f = _fn("recurrence", "vob_recurrence_scan", [_I, _P, _L, _P, _L, _I, _P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
     _check(f(mode, _ptr(r), r.stride(0), _ptr(k), k.stride(0), _code(r, op), _ptr(v), v.stride(0), _code(v, op), _ptr(w), _ptr(b), _ptr(u),
-             _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), num_seqs, heads, K, V, _stream()), op)
+             _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), num_seqs, heads, K, V, heads // rk_heads, _stream()), op)
 
 
 @_timed
 def recurrence_post(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], gate_mode: str, eps: float, heads: int,
-                    out: torch.Tensor) -> None:
-    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate), head by head; act is "sigmoid" or "silu".
-    o float32 [T, heads * V]; gate [T, heads * V] (any row stride) and out (contiguous) in the activations' type."""
+                    out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) * out_scale, head by head; act is "sigmoid" or "silu".
+    o float32 [T, heads * V]; gate and out [T, heads * V] (any row stride) in the activations' type."""
     op = "recurrence_post"
     _cuda(op, o, gate, weight, out)
     _rows_2d(gate, op, "gate")
+    _rows_2d(out, op, "out")
     T, hv = o.shape
     if o.dtype != torch.float32 or not o.is_contiguous() or hv % heads != 0:
         raise ShapeError(op, f"o must be contiguous float32 [T, heads * V], got {o.dtype} {list(o.shape)}")
-    if gate.shape != (T, hv) or out.shape != (T, hv) or out.dtype != gate.dtype or not out.is_contiguous():
+    if gate.shape != (T, hv) or out.shape != (T, hv) or out.dtype != gate.dtype:
         raise ShapeError(op, f"gate and out must be [{T}, {hv}] of one type, got {list(gate.shape)} and {list(out.shape)}")
     _f32_vec(weight, hv, op, "weight")
     if gate_mode not in ("sigmoid", "silu"):
         raise ShapeError(op, f"gate {gate_mode!r} is not known (sigmoid or silu)")
-    f = _fn("recurrence", "vob_recurrence_post", [_P, _P, _I, _L, _P, _I, _F, _I, _I, _I, _P, _P])
+    f = _fn("recurrence", "vob_recurrence_post", [_P, _P, _I, _L, _P, _I, _F, _I, _I, _I, _P, _L, _F, _P])
     _check(f(_ptr(o), _ptr(gate), _code(gate, op), gate.stride(0), _ptr(weight), 1 if gate_mode == "silu" else 0, float(eps), T, heads,
-             hv // heads, _ptr(out), _stream()), op)
+             hv // heads, _ptr(out), out.stride(0), float(out_scale), _stream()), op)
+
+
+@_timed
+def gated_delta_prep(proj: torch.Tensor, x_off: int, b_off: int, low: torch.Tensor, a_off: int, conv_w: torch.Tensor,
+                     conv_state: Optional[torch.Tensor], a_log: torch.Tensor, dt_bias: torch.Tensor, positions: torch.Tensor,
+                     row_seq: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, heads: int,
+                     rk_heads: int, dim: int, vdim: int, q_out: torch.Tensor, k_out: torch.Tensor, v_out: torch.Tensor,
+                     decay: torch.Tensor, strength: torch.Tensor) -> None:
+    """What the gated delta rule reads, per token. Columns x_off.. of `proj` [T, ld] hold q, k (rk_heads heads of
+    `dim` each) and v (heads of `vdim`) side by side: each channel passes a causal convolution over the request's
+    tokens (conv_w float32 [C, taps], last column the current token's; inputs before the step's first row from
+    conv_state float32 [slots, taps - 1, C]) and silu; q and k are then scaled to unit length per head (1e-6 under
+    the root), q also by dim^-1/2. strength = sigmoid(proj[b_off + h]); decay = exp(-exp(a_log[h]) *
+    softplus(low[a_off + h * dim + c] + dt_bias)). q_out, k_out float32 [T, rk_heads * dim]; v_out [T, heads * vdim]
+    in proj's type; decay float32 [T, heads * dim]; strength float32 [T, heads]."""
+    op = "gated_delta_prep"
+    _cuda(op, proj, low, conv_w, conv_state, a_log, dt_bias, positions, row_seq, seq_starts, state_slots, q_out, k_out, v_out, decay, strength)
+    _rows_2d(proj, op, "proj")
+    _rows_2d(low, op, "low")
+    T = proj.shape[0]
+    C = 2 * rk_heads * dim + heads * vdim
+    if conv_w.dtype != torch.float32 or conv_w.dim() != 2 or conv_w.shape[0] != C or not conv_w.is_contiguous():
+        raise ShapeError(op, f"conv_w must be contiguous float32 [{C}, taps], got {conv_w.dtype} {list(conv_w.shape)}")
+    taps = conv_w.shape[1]
+    if taps > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 3 or conv_state.shape[1:] != (taps - 1, C)
+                     or not conv_state.is_contiguous()):
+        raise ShapeError(op, f"conv_state must be contiguous float32 [slots, {taps - 1}, {C}]")
+    if low.dtype != proj.dtype or low.shape[0] != T or a_off < 0 or a_off + heads * dim > low.shape[1]:
+        raise ShapeError(op, f"low must be {proj.dtype} [{T}, >= {a_off + heads * dim}], got {low.dtype} {list(low.shape)}")
+    if x_off < 0 or x_off + C > proj.shape[1] or b_off < 0 or b_off + heads > proj.shape[1]:
+        raise ShapeError(op, f"columns {x_off}..{x_off + C} or {b_off}..{b_off + heads} lie outside proj's {proj.shape[1]}")
+    _f32_vec(a_log, heads, op, "a_log")
+    _f32_vec(dt_bias, heads * dim, op, "dt_bias")
+    for name, t, cols in (("q_out", q_out, rk_heads * dim), ("k_out", k_out, rk_heads * dim), ("decay", decay, heads * dim),
+                          ("strength", strength, heads)):
+        if t.dtype != torch.float32 or t.shape != (T, cols) or not t.is_contiguous():
+            raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {cols}], got {t.dtype} {list(t.shape)}")
+    if v_out.dtype != proj.dtype or v_out.shape != (T, heads * vdim) or not v_out.is_contiguous():
+        raise ShapeError(op, f"v_out must be contiguous {proj.dtype} [{T}, {heads * vdim}], got {v_out.dtype} {list(v_out.shape)}")
+    _int32_vec(positions, T, op, "positions")
+    _int32_vec(row_seq, T, op, "row_seq")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(state_slots, num_seqs, op, "state_slots")
+    f = _fn("recurrence", "vob_gated_delta_prep", [_P, _I, _L, _I, _I, _P, _L, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                                                   _P, _P, _P, _P, _P, _P])
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), x_off, b_off, _ptr(low), low.stride(0), a_off, _ptr(conv_w), taps,
+             _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(positions), _ptr(row_seq), _ptr(seq_starts), _ptr(state_slots), T,
+             heads, rk_heads, dim, vdim, _ptr(q_out), _ptr(k_out), _ptr(v_out), _ptr(decay), _ptr(strength), _stream()), op)
+
+
+@_timed
+def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor,
+                      num_seqs: int) -> None:
+    """Leave every request's last taps - 1 convolution inputs (columns x_off .. x_off + C - 1 of proj) in its state slot;
+    a request that brought fewer rows keeps the newest of what it had. conv_state float32 [slots, taps - 1, C]."""
+    op = "conv_state_update"
+    _cuda(op, proj, conv_state, seq_starts, state_slots)
+    _rows_2d(proj, op, "proj")
+    if conv_state.dtype != torch.float32 or conv_state.dim() != 3 or not conv_state.is_contiguous():
+        raise ShapeError(op, f"conv_state must be contiguous float32 [slots, taps - 1, C], got {conv_state.dtype} {list(conv_state.shape)}")
+    C = conv_state.shape[2]
+    if x_off < 0 or x_off + C > proj.shape[1]:
+        raise ShapeError(op, f"columns {x_off}..{x_off + C} lie outside proj's {proj.shape[1]}")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(state_slots, num_seqs, op, "state_slots")
+    f = _fn("recurrence", "vob_conv_state_update", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _P])
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), x_off, C, conv_state.shape[1] + 1, _ptr(conv_state), _ptr(seq_starts),
+             _ptr(state_slots), num_seqs, _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention over a latent cache
@@ -944,6 +1059,95 @@ def latent_attend_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor
     _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _ptr(block_tables), block_tables.shape[1],
              _ptr(seq_starts), _ptr(positions), lat.shape[2], int(num_seqs), int(max_new), H, L, R, float(scale), _ptr(out), out.stride(0),
              out.stride(1), _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ attention with options
+def _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, dtype):
+    for name, c, w in (("kcache", kcache, dim), ("vcache", vcache, vdim)):
+        if c.dim() != 4 or c.shape[1] != kv_heads or c.shape[3] != w or not c.is_contiguous() or c.dtype != dtype:
+            raise ShapeError(op, f"{name} must be contiguous {dtype} [pages, {kv_heads}, page_size, {w}], got {c.dtype} {list(c.shape)}")
+    if kcache.shape[:3] != vcache.shape[:3]:
+        raise ShapeError(op, "kcache and vcache differ in pages, heads or page size")
+    if kcache.numel() // dim >= 2 ** 31:
+        raise ShapeError(op, "one layer's cache has 2^31 rows or more")
+
+
+@_timed
+def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions: torch.Tensor, slots: Optional[torch.Tensor],
+              inv_freq: Optional[torch.Tensor], rot: int, unit_rms: bool, eps: float, q_temp, vmix: Optional[torch.Tensor],
+              v_first: Optional[torch.Tensor], v_mode: int, q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+              heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+    """Per token, from the columns q_off.., k_off.., v_off.. of `proj`: q and k with their first `rot` features rotated
+    (feature i with i + rot / 2, by position * inv_freq[i]), then (unit_rms) divided by sqrt(mean(x^2) + eps) per head;
+    q times 1 + coef * ln(floor((pos + 1) / every) + 1) for q_temp = (coef, every). q goes to q_out [T, heads * dim], k
+    and v to their cache slots. v_mode 1 also leaves v in v_first [T, kv_heads * vdim]; v_mode 2 mixes
+    v <- (1 - vmix) v + vmix v_first before the write (vmix: one float32 on the device)."""
+    op = "flex_prep"
+    _cuda(op, proj, positions, slots, inv_freq, vmix, v_first, q_out, kcache, vcache)
+    _rows_2d(proj, op, "proj")
+    _rows_2d(q_out, op, "q_out")
+    T = proj.shape[0]
+    for off, n in ((q_off, heads * dim), (k_off, kv_heads * dim), (v_off, kv_heads * vdim)):
+        if off < 0 or off + n > proj.shape[1]:
+            raise ShapeError(op, f"columns {off}..{off + n} lie outside proj's {proj.shape[1]}")
+    if q_out.shape != (T, heads * dim) or q_out.dtype != proj.dtype:
+        raise ShapeError(op, f"q_out must be {proj.dtype} [{T}, {heads * dim}], got {q_out.dtype} {list(q_out.shape)}")
+    _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, proj.dtype)
+    _int32_vec(positions, T, op, "positions")
+    if slots is not None:
+        _int32_vec(slots, T, op, "slots")
+    if rot:
+        _f32_vec(inv_freq, rot // 2, op, "inv_freq")
+    if v_mode not in (0, 1, 2):
+        raise ShapeError(op, f"v_mode {v_mode} is not known")
+    if v_mode and (v_first is None or v_first.dtype != proj.dtype or v_first.shape != (T, kv_heads * vdim) or not v_first.is_contiguous()):
+        raise ShapeError(op, f"v_first must be contiguous {proj.dtype} [{T}, {kv_heads * vdim}]")
+    if v_mode == 2:
+        _f32_vec(vmix, 1, op, "vmix")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    f = _fn("attention_flex", "vob_flex_prep", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P, _P, _I, _P, _L, _P, _P,
+                                                _I, _I, _I, _I, _I, _I, _P])
+    _check(f(_ptr(proj), _code(proj, op), proj.stride(0), q_off, k_off, v_off, _ptr(positions), _ptr(slots), _ptr(inv_freq), int(rot),
+             1 if unit_rms else 0, float(eps), coef, every, _ptr(vmix), _ptr(v_first), int(v_mode), _ptr(q_out), q_out.stride(0),
+             _ptr(kcache), _ptr(vcache), T, heads, kv_heads, dim, vdim, kcache.shape[2], _stream()), op)
+
+
+@_timed
+def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                   row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                   window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                   out_scale: float = 1.0) -> None:
+    """Causal attention of every row of q [T, heads * dim] over its request's pages, keys of `dim` and values of `vdim`
+    features: out [T, heads * vdim] (any row stride) = softmax(q . K * scale) V, over the last `window` keys (0: all), the
+    denominator also holding exp(sink[head]) if `sink` (float32 [heads]) is given; times sigmoid(gate) ([T, heads * vdim],
+    any row stride) and `out_scale`."""
+    op = "flex_attention"
+    _cuda(op, q, out, kcache, vcache, block_tables, row_seq, positions, sink, gate)
+    _rows_2d(q, op, "q")
+    _rows_2d(out, op, "out")
+    T = q.shape[0]
+    if q.shape[1] != heads * dim or out.shape != (T, heads * vdim) or out.dtype != q.dtype:
+        raise ShapeError(op, f"q [{T}, {heads * dim}] and out [{T}, {heads * vdim}] of one dtype are needed, got {list(q.shape)} "
+                             f"{q.dtype} and {list(out.shape)} {out.dtype}")
+    if kv_heads <= 0 or heads % kv_heads != 0:
+        raise ShapeError(op, f"{heads} heads are not a multiple of {kv_heads} kv heads")
+    if dim > 256 or vdim > 256:
+        raise ShapeError(op, f"head sizes {dim} / {vdim} are beyond this kernel's 256")
+    _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, q.dtype)
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, f"block_tables must be contiguous int32 [S, max_pages], got {block_tables.dtype} {list(block_tables.shape)}")
+    _int32_vec(row_seq, T, op, "row_seq")
+    _int32_vec(positions, T, op, "positions")
+    _f32_vec(sink, heads, op, "sink")
+    if gate is not None:
+        _rows_2d(gate, op, "gate")
+        if gate.shape != (T, heads * vdim) or gate.dtype != q.dtype:
+            raise ShapeError(op, f"gate must be {q.dtype} [{T}, {heads * vdim}], got {gate.dtype} {list(gate.shape)}")
+    f = _fn("attention_flex", "vob_flex_attention", [_P, _L, _P, _L, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P,
+                                                     _L, _F, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _code(q, op), _ptr(block_tables),
+             block_tables.shape[1], _ptr(row_seq), _ptr(positions), T, heads, kv_heads, dim, vdim, kcache.shape[2], int(window),
+             float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention

@@ -1,5 +1,7 @@
 """Architectures this engine knows. Importing the package registers them."""
 from .llama import LLAMA, BuildContext, build_llama, llama_manifest
 from .rotepel import ROTEPEL, build_rotepel, rotepel_manifest
+from .lomopel import LOMOPEL, build_lomopel, lomopel_manifest
 
-__all__ = ["LLAMA", "BuildContext", "build_llama", "llama_manifest", "ROTEPEL", "build_rotepel", "rotepel_manifest"]
+__all__ = ["LLAMA", "BuildContext", "build_llama", "llama_manifest", "ROTEPEL", "build_rotepel", "rotepel_manifest",
+           "LOMOPEL", "build_lomopel", "lomopel_manifest"]

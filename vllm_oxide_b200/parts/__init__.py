@@ -7,10 +7,12 @@ from .swiglu import SwiGLU
 from .embedding import Embedding, LMHead
 from .block import Block
 from .streams import PendingWrite, StreamBlock, StreamCoefficients, StreamEmbedding, StreamNorm
-from .recurrent import GeneralDelta, Retention
+from .recurrent import GatedDelta, GeneralDelta, Retention
+from .flex_attention import SoftmaxAttention
+from .parallel import ParallelMixer
 from .latent_attention import LatentAttention
 
 __all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
            "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
            "SwiGLU", "Embedding", "LMHead", "Block", "PendingWrite", "StreamBlock", "StreamCoefficients", "StreamEmbedding",
-           "StreamNorm", "GeneralDelta", "Retention", "LatentAttention"]
+           "StreamNorm", "GeneralDelta", "Retention", "LatentAttention", "GatedDelta", "SoftmaxAttention", "ParallelMixer"]

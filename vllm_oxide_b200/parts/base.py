@@ -10,7 +10,8 @@ in a `StepContext`.
 What each kind of part must offer:
 
 * Mixer        - `cache_spec()` (pages it needs: which tensors a page holds, for all keys or a
-                 window of them; or None), `state_spec()` (fixed-size per-request state, or None),
+                 window of them; or None), `state_spec()` (fixed-size per-request state: one
+                 `StateSpec`, a tuple of them, or None),
                  `forward(x, ctx, cache, state, out=None) -> [T, hidden]` in the compute dtype.
 * FeedForward  - `forward(x, ctx, out=None) -> [T, hidden]`.
 * Norm         - `forward(resid, delta, ctx, rows=None) -> normed`; adds `delta` into the
@@ -22,8 +23,8 @@ engine compiles them at its start) and `weight_bytes()`.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -64,7 +65,9 @@ class CacheSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Fixed-size state per request: one tensor of `shape` per state slot, zeroed at admission."""
+    """Fixed-size state per request: one tensor of `shape` per state slot, zeroed at admission. A mixer
+    whose state is several tensors (a matrix and the last inputs of a convolution, say) returns a tuple
+    of these from `state_spec()` and gets a tuple of tensors in the same order."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
@@ -177,6 +180,8 @@ class StepContext:
     long_context: bool = False      # some request is longer than TUNING.long_context_keys (host fact; a replayed
                                     # step was recorded with the same value)
     host: Optional[object] = None   # the host-side StepArrays (ids, counts) for parts that want them
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)   # what one layer of this step leaves for later layers of
+                                    # the same step, by name: the buffers `ModelSpec.step_buffers` names, one row per row
 
     def alloc(self, shape, dtype=None) -> torch.Tensor:
         return self.workspace.alloc(shape, dtype or self.dtype)
@@ -203,7 +208,8 @@ class Mixer:
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 
-    def state_spec(self) -> Optional[StateSpec]:
+    def state_spec(self):
+        """None, one `StateSpec`, or a tuple of them."""
         return None
 
     def workspace_bytes(self, rows: int) -> int:
@@ -245,7 +251,10 @@ class Norm:
         return ()
 
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
-                rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None,
+                delta_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`delta_scale` (float32 [hidden], only passed where a block has one): the delta is multiplied
+        by it, feature by feature, before it is added."""
         raise NotImplementedError
 
 
@@ -277,3 +286,6 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     weight_bytes: int = 0               # bytes a decode step must read of the weights
     residual_streams: int = 1           # the residual is float32 [rows, residual_streams * hidden_size]
+    # buffers that live for one step and that layers hand to later layers through `StepContext.shared`:
+    # name -> (columns, dtype or None for the compute dtype); [rows, columns] each, allocated behind the embedding
+    step_buffers: Dict[str, Tuple[int, Optional[torch.dtype]]] = field(default_factory=dict)

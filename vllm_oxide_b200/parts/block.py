@@ -4,6 +4,11 @@
 (crates/engine/src/model.rs:302-332). The residual is float32. Each part's output is not added
 at once: it is handed on as `pending` and the next norm's kernel adds it while it normalises
 (one pass over the row instead of two). The model's final norm takes the last `pending`.
+
+Options: a per-feature scale on each part's output before it is added (`mixer_scale`, `ff_scale`:
+the norm's kernel multiplies while it adds; `pending_scale` tells whoever adds this block's
+output which one goes with it), and a block without a feed-forward (`feed_forward` None:
+    residual += mixer(norm1(residual)) only; `norm2` is None then).
 """
 from __future__ import annotations
 
@@ -15,16 +20,34 @@ from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StepContext
 
 
 class Block:
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], feed_forward: Optional[FeedForward],
+                 mixer_scale: Optional[torch.Tensor] = None, ff_scale: Optional[torch.Tensor] = None):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        if (norm2 is None) != (feed_forward is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        dev = getattr(norm1, "weight", None)
+
+        def vec(t):
+            if t is None:
+                return None
+            return t.to(device=dev.device if dev is not None else t.device, dtype=torch.float32).contiguous()
+        self.mixer_scale, self.ff_scale = vec(mixer_scale), vec(ff_scale)
+        # the scale that goes with the output this block hands on
+        self.pending_scale = self.ff_scale if feed_forward is not None else self.mixer_scale
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
     def weight_bytes(self) -> int:
-        return sum(getattr(p, "weight_bytes", lambda: 0)() for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+        scales = sum(t.numel() * 4 for t in (self.mixer_scale, self.ff_scale) if t is not None)
+        return scales + sum(getattr(p, "weight_bytes", lambda: 0)() for p in self._parts())
 
     def workspace_bytes(self, rows: int, hidden: int, act_bytes: int) -> int:
         """Peak scratch of one run of the block, read off the scopes of `forward`: the mixer's
         output, then the larger of (first norm's output + mixer scratch) and (second norm's output +
         feed-forward scratch)."""
+        if self.feed_forward is None:
+            return self.norm1.workspace_bytes(rows, act_bytes) + self.mixer.workspace_bytes(rows)
         mixed = aligned(rows * hidden * act_bytes)
         return mixed + max(self.norm1.workspace_bytes(rows, act_bytes) + self.mixer.workspace_bytes(rows),
                            self.norm2.workspace_bytes(rows, act_bytes) + self.feed_forward.workspace_bytes(rows))
@@ -36,7 +59,7 @@ class Block:
 
     def kernel_modules(self, dtype, max_rows):
         mods = []
-        for p in (self.norm1, self.mixer, self.norm2, self.feed_forward):
+        for p in self._parts():
             mods += list(getattr(p, "kernel_modules", lambda d, r: ())(dtype, max_rows))
         return tuple(mods)
 
@@ -44,6 +67,8 @@ class Block:
         """Whether this block can run in folded form (see FoldedState): both norms are a per-token
         scale and a per-feature weight (`Norm.scale_and_weight`), which is what folds into the
         neighbouring products, and mixer and feed-forward both offer it."""
+        if self.feed_forward is None or self.mixer_scale is not None or self.ff_scale is not None:
+            return False
         return (self.norm1.scale_and_weight and self.norm2.scale_and_weight
                 and getattr(self.mixer, "can_fold", lambda: False)() and getattr(self.feed_forward, "can_fold", lambda: False)()
                 and self.mixer.state_spec() is None)
@@ -58,19 +83,32 @@ class Block:
             self.feed_forward.forward_folded(st, self.norm2.eps, ctx, next_norm.weight)
 
     def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+                cache: Optional[LayerCache], state, out: torch.Tensor, pending_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the block. `pending` is the previous block's output that is still to be added to
-        the residual; the feed-forward's output (again not yet added) is written to `out`,
-        which outlives the block's own scratch."""
+        the residual (times `pending_scale`, if that block had one); the feed-forward's output
+        (again not yet added) is written to `out`, which outlives the block's own scratch."""
         ws = ctx.workspace
+
+        def first_norm():
+            if pending is not None and pending_scale is not None:
+                return self.norm1.forward(resid, pending, ctx, delta_scale=pending_scale)
+            return self.norm1.forward(resid, pending, ctx)
+        if self.feed_forward is None:
+            with ws.scope():
+                m = self.mixer.forward(first_norm(), ctx, cache, state, out=out)
+                if m.data_ptr() != out.data_ptr():
+                    out.copy_(m)
+            return out
         with ws.scope():
             mixed = ctx.alloc(out.shape, out.dtype)
             with ws.scope():
-                normed = self.norm1.forward(resid, pending, ctx)
-                m = self.mixer.forward(normed, ctx, cache, state, out=mixed)
+                m = self.mixer.forward(first_norm(), ctx, cache, state, out=mixed)
                 if m.data_ptr() != mixed.data_ptr():
                     mixed.copy_(m)
-            normed2 = self.norm2.forward(resid, mixed, ctx)
+            if self.mixer_scale is not None:
+                normed2 = self.norm2.forward(resid, mixed, ctx, delta_scale=self.mixer_scale)
+            else:
+                normed2 = self.norm2.forward(resid, mixed, ctx)
             ff = self.feed_forward.forward(normed2, ctx, out=out)
             if ff.data_ptr() != out.data_ptr():
                 out.copy_(ff)

@@ -12,8 +12,10 @@ from .linear import to_compute
 
 
 class Embedding:
-    def __init__(self, table: torch.Tensor, dtype=torch.bfloat16, device="cuda"):
+    def __init__(self, table: torch.Tensor, dtype=torch.bfloat16, device="cuda", scale: float = 1.0):
+        """`scale`: every row is multiplied by it on its way into the float32 residual."""
         self.table = to_compute(table, dtype, device)
+        self.scale = float(scale)
         self.vocab, self.hidden = self.table.shape
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -22,7 +24,7 @@ class Embedding:
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         resid = ctx.alloc((ctx.rows, self.hidden), torch.float32)
-        kernels.embed(self.table, ctx.tokens, resid, self.err_flag)
+        kernels.embed(self.table, ctx.tokens, resid, self.err_flag, self.scale)
         return resid
 
     def forward_folded(self, ctx: StepContext, next_norm) -> FoldedState:

@@ -13,14 +13,23 @@ at zero when the request is admitted and is carried from token to token across s
     q, k = rotary(W_q h), rotary(W_k h) * dim^-1/2;   v = W_v h  (heads of `vdim`)
     S_t = decay_h S_(t-1) + k v^T;   o = S_t^T q;   out = W_o (rms_head(o) * silu(W_g h))
 
-Both run the same scan kernel (`kernels.recurrence_scan`) for prompt portions and single tokens
+`GatedDelta`, the gated delta rule, per value head (keys of `dim`, values of `vdim`; several value heads
+may share one q and k head):
+    q, k, v = silu(conv(W_q h)), silu(conv(W_k h)), silu(conv(W_v h))     short causal convolutions per channel
+    q = q / sqrt(sum q^2 + 1e-6) * dim^-1/2;   k = k / sqrt(sum k^2 + 1e-6)
+    beta = sigmoid(W_b h);   g = exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias))   decay per key channel
+    S' = diag(g) S_(t-1);   S_t = S' + k (beta (v - S'^T k))^T;   o = S_t^T q
+    out = W_o (rms_head(o) * norm_weight * sigmoid(W_g2 W_g1 h))
+Its state is the matrix S and, in a second tensor, the convolutions' last taps - 1 inputs.
+
+All run the same scan kernel (`kernels.recurrence_scan`) for prompt portions and single tokens
 alike. The projections are one matrix product each side of it, in the compute dtype; everything
 between them that enters the recurrence (unit key, decay, removal rate, rotation, the state, the
 per-head norm and the gates) is float32.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -130,3 +139,96 @@ class Retention(Mixer):
         gated = ctx.alloc((T, hv))
         kernels.recurrence_post(o, proj[:, 2 * hk + hv:], None, "silu", self.eps, self.H, gated)
         return matmul(gated, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
+
+
+class GatedDelta(Mixer):
+    """See the module's head. `conv_q`, `conv_k`, `conv_v` are [channels, taps] with the last column the
+    current token's. `w_a1` / `w_a2` and `w_g1` / `w_g2` are the two low-rank pairs (decay and output gate);
+    `norm_weight` [vdim] is shared by the heads. Like `SoftmaxAttention` it offers its halves separately
+    (`w_in`, `core`, `w_o`) for a layer that runs it beside another mixer."""
+
+    def __init__(self, wq, wk, wv, conv_q, conv_k, conv_v, wb, a_log, w_a1, w_a2, dt_bias, w_g1, w_g2, norm_weight, wo, heads: int,
+                 kv_heads: int, dim: int, vdim: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+        self.H, self.G, self.K, self.V = int(heads), int(kv_heads), int(dim), int(vdim)
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.G} q/k heads")
+        if self.K > 512:
+            raise ValueError(f"a key size of {self.K} is beyond the scan's 512")
+        hidden = wq.shape[1]
+        gk, hk, hv = self.G * self.K, self.H * self.K, self.H * self.V
+        if wq.shape != (gk, hidden) or wk.shape != (gk, hidden) or wv.shape != (hv, hidden) or wb.shape != (self.H, hidden) or wo.shape != (hidden, hv):
+            raise ValueError(f"projection shapes do not fit {self.H} heads on {self.G} of {self.K} / {self.V} over a width of {hidden}")
+        self.taps = conv_q.shape[1]
+        for name, c, n in (("q", conv_q, gk), ("k", conv_k, gk), ("v", conv_v, hv)):
+            if c.shape != (n, self.taps):
+                raise ValueError(f"convolution '{name}' is {list(c.shape)}, expected [{n}, {self.taps}]")
+        ra, rg = w_a1.shape[0], w_g1.shape[0]
+        if w_a1.shape != (ra, hidden) or w_a2.shape != (hk, ra) or w_g1.shape != (rg, hidden) or w_g2.shape != (hv, rg):
+            raise ValueError(f"low-rank projections {list(w_a1.shape)} / {list(w_a2.shape)} / {list(w_g1.shape)} / {list(w_g2.shape)} do not fit")
+        if a_log.shape != (self.H,) or dt_bias.shape != (hk,) or norm_weight.shape != (self.V,):
+            raise ValueError("A_log [heads], dt_bias [heads * dim] and the norm weight [vdim] are needed")
+        self.C = 2 * gk + hv
+        # one matrix [Wq; Wk; Wv; Wa1; Wg1; Wb]: q, k, v side by side (the convolutions' channels), then the
+        # two low-rank inputs side by side (one second product serves both), the strengths last
+        self.w_in = to_compute(torch.cat([wq, wk, wv, w_a1, w_g1, wb], dim=0), dtype, device)
+        self.low_off, self.ra, self.rg = self.C, ra, rg
+        self.b_off = self.C + ra + rg
+        self.b_in = None
+        # [[Wa2, 0], [0, Wg2]]: the zero blocks add exact zeros, so each half is the product of its own pair
+        low = torch.zeros(hk + hv, ra + rg, dtype=torch.float32, device=w_a2.device)
+        low[:hk, :ra] = w_a2.float()
+        low[hk:, ra:] = w_g2.float().to(low.device)
+        self.w_low = to_compute(low, dtype, device)
+        self.w_o = to_compute(wo, dtype, device)
+        self.b_o = None
+        self.n_pre = hv
+        f32 = dict(device=device, dtype=torch.float32)
+        self.conv_w = torch.cat([conv_q.to(**f32), conv_k.to(**f32), conv_v.to(**f32)], dim=0).contiguous()
+        self.a_log, self.dt_bias = a_log.to(**f32).contiguous(), dt_bias.to(**f32).contiguous()
+        self.norm_weight = norm_weight.to(**f32).repeat(self.H).contiguous()        # the kernel takes one weight per head and feature
+        self.eps, self.hidden, self.dtype = float(eps), hidden, dtype
+
+    def state_spec(self):
+        s = StateSpec((self.H, self.K, self.V), torch.float32)
+        return (s, StateSpec((self.taps - 1, self.C), torch.float32)) if self.taps > 1 else (s,)
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_low.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def core_workspace_bytes(self, rows: int) -> int:
+        es, gk, hk, hv = self.w_in.element_size(), self.G * self.K, self.H * self.K, self.H * self.V
+        return (aligned(rows * (hk + hv) * es) + 2 * aligned(rows * gk * 4) + aligned(rows * hv * es) + aligned(rows * hk * 4)
+                + aligned(rows * self.H * 4) + aligned(rows * hv * 4))
+
+    def workspace_bytes(self, rows: int) -> int:
+        es = self.w_in.element_size()
+        return aligned(rows * self.w_in.shape[0] * es) + aligned(rows * self.n_pre * es) + self.core_workspace_bytes(rows)
+
+    def kernel_modules(self, dtype, max_rows):
+        return _modules(dtype)
+
+    def core(self, proj: torch.Tensor, ctx: StepContext, cache, state, pre_out: torch.Tensor, out_scale: float = 1.0) -> None:
+        """proj [T, >= w_in rows] -> pre_out [T, heads * vdim]: everything between the two projections."""
+        if state is None:
+            raise ValueError("the gated delta rule needs its state")
+        S, conv_state = state[0], (state[1] if self.taps > 1 else None)
+        T, gk, hk, hv = proj.shape[0], self.G * self.K, self.H * self.K, self.H * self.V
+        low = ctx.alloc((T, hk + hv))
+        kernels.linear(proj[:, self.low_off:self.low_off + self.ra + self.rg], self.w_low, low)
+        q, k = ctx.alloc((T, gk), torch.float32), ctx.alloc((T, gk), torch.float32)
+        v = ctx.alloc((T, hv))
+        decay, strength = ctx.alloc((T, hk), torch.float32), ctx.alloc((T, self.H), torch.float32)
+        kernels.gated_delta_prep(proj, 0, self.b_off, low, 0, self.conv_w, conv_state, self.a_log, self.dt_bias, ctx.positions, ctx.row_seq,
+                                 ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, self.G, self.K, self.V, q, k, v, decay, strength)
+        if conv_state is not None:
+            kernels.conv_state_update(proj, 0, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
+        o = ctx.alloc((T, hv), torch.float32)
+        kernels.recurrence_scan(2, q, k, v, decay, strength, None, S, ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, o, rk_heads=self.G)
+        kernels.recurrence_post(o, low[:, hk:], self.norm_weight, "sigmoid", self.eps, self.H, pre_out, out_scale)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state, out=None) -> torch.Tensor:
+        T = x.shape[0]
+        proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
+        pre = ctx.alloc((T, self.n_pre))
+        self.core(proj, ctx, cache, state, pre)
+        return matmul(pre, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))

@@ -18,11 +18,15 @@ from .base import Norm, StepContext, aligned
 class RMSNorm(Norm):
     scale_and_weight = True       # out = weight * (x * scale(x)): folds into the products around it
 
-    def __init__(self, weight: torch.Tensor, eps: float, device):
+    def __init__(self, weight: torch.Tensor, eps: float, device, unit_offset: bool = False):
+        """`unit_offset`: the stored weight lies around zero and the factor is 1 + weight (the sum is
+        taken once, here, in float32)."""
         if weight.dim() != 1:
             raise ValueError(f"RMSNorm weight must be a vector, got {list(weight.shape)}")
         # The weight is read as float32 whatever it was stored as (widening is exact).
         self.weight = weight.to(device=device, dtype=torch.float32).contiguous()
+        if unit_offset:
+            self.weight = (self.weight + 1.0).contiguous()
         self.eps = float(eps)
         self.width = weight.shape[0]
 
@@ -36,8 +40,10 @@ class RMSNorm(Norm):
         return ("elementwise",)
 
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
-                rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, num_rows: Optional[int] = None,
+                delta_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = resid.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = ctx.alloc((n, self.width))
-        kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows[:n] if rows is not None else None)
+        kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows[:n] if rows is not None else None,
+                            delta_scale if delta is not None else None)
         return out

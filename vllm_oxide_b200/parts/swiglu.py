@@ -1,6 +1,8 @@
-"""SwiGLU feed-forward: down(silu(gate(x)) * up(x)), dense, no bias
-(crates/engine/src/model.rs:325-331; activation crates/engine/src/backend/cpu/mod.rs:341-349).
-gate and up are one fused matrix [Wgate; Wup], so a single product feeds the activation."""
+"""Gated feed-forward: down(act(gate(x)) * up(x)), dense, no bias; act is silu (SwiGLU,
+crates/engine/src/model.rs:325-331; activation crates/engine/src/backend/cpu/mod.rs:341-349) or,
+with `activation="gelu_tanh"`, the tanh form of gelu. gate and up are one fused matrix
+[Wgate; Wup], so a single product feeds the activation. The products whose epilogue applies the
+activation are built for silu; any other activation runs the product and the activation kernel."""
 from __future__ import annotations
 
 import torch
@@ -12,8 +14,12 @@ from .linear import matmul, to_compute
 
 
 class SwiGLU(FeedForward):
-    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, dtype=torch.bfloat16, device="cuda"):
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, dtype=torch.bfloat16, device="cuda",
+                 activation: str = "silu"):
         inter, hidden = w_gate.shape
+        if activation not in kernels.GLU_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not known ({', '.join(kernels.GLU_ACTIVATIONS)})")
+        self.activation = activation
         if w_up.shape != (inter, hidden) or w_down.shape != (hidden, inter):
             raise ValueError(f"feed-forward shapes do not fit: gate {list(w_gate.shape)}, up {list(w_up.shape)}, "
                              f"down {list(w_down.shape)}")
@@ -30,7 +36,7 @@ class SwiGLU(FeedForward):
         """Which kernels a step of `rows` rows runs: "few" (one tcgen05 kernel, activation in its
         epilogue), "pair" (the two-SM product with the activation in its epilogue) or "separate"
         (a product to gate|up, then the activation kernel)."""
-        ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0
+        ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0 and self.activation == "silu"
         if ok and rows <= TUNING.few_rows:
             return "few"
         if ok and rows >= TUNING.pair_gemm_from_rows:
@@ -61,7 +67,8 @@ class SwiGLU(FeedForward):
         return tuple(mods)
 
     def can_fold(self) -> bool:
-        return self.dtype == torch.bfloat16 and self.fused and self.hidden % 8 == 0 and self.inter % 8 == 0
+        return (self.dtype == torch.bfloat16 and self.fused and self.hidden % 8 == 0 and self.inter % 8 == 0
+                and self.activation == "silu")
 
     def forward_folded(self, st: FoldedState, eps: float, ctx: StepContext, next_w: torch.Tensor) -> None:
         """gate/up product with the preceding norm folded in and the activation in its epilogue;
@@ -84,5 +91,5 @@ class SwiGLU(FeedForward):
             kernels.gemm_pair_swiglu(x, self.w_gate_up, act)
         else:
             gate_up = matmul(x, self.w_gate_up, ctx.alloc((T, 2 * self.inter)))
-            kernels.swiglu(gate_up, act)
+            kernels.glu(gate_up, act, self.activation)
         return matmul(act, self.w_down, out if out is not None else ctx.alloc((T, self.hidden)))

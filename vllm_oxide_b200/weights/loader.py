@@ -29,10 +29,13 @@ _INT_NAMES = ("I8", "U8", "I16", "I32", "I64")
 @dataclass(frozen=True)
 class TensorSpec:
     """What the model expects under one name. A dimension of -1 is not fixed by the configuration:
-    whatever the stored tensor has there is taken (such a tensor cannot be drawn at random)."""
+    whatever the stored tensor has there is taken (such a tensor cannot be drawn at random).
+    `optional`: a tensor the model does not use but a checkpoint may hold (it is accepted and may be
+    absent; random weights leave it out)."""
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" or "int"
     init: str = "normal"         # random-weights rule: "normal", "ones", "zeros" or "identity"
+    optional: bool = False
 
 
 class WeightSet:
@@ -51,6 +54,11 @@ class WeightSet:
 
     def has(self, name: str) -> bool:
         return name in self._tensors
+
+    def skip(self, name: str) -> None:
+        """Mark a tensor the model has no use for (an optional one) as dealt with."""
+        if name in self._tensors:
+            self._taken.add(name)
 
     def finish(self) -> None:
         left = set(self._tensors) - self._taken
@@ -76,7 +84,7 @@ def check_against_manifest(source: str, found: Mapping[str, Tuple[Tuple[int, ...
                            manifest: Mapping[str, TensorSpec]) -> None:
     """Raise one WeightsError for everything in `found` ({name: (shape, dtype name)}) that
     does not fit `manifest`."""
-    missing = [n for n in manifest if n not in found]
+    missing = [n for n in manifest if n not in found and not manifest[n].optional]
     unexpected = [n for n in found if n not in manifest]
     wrong_shape, wrong_dtype = [], []
     for n, spec in manifest.items():
@@ -133,6 +141,8 @@ def load_safetensors_weights(model_dir: str, manifest: Mapping[str, TensorSpec],
     check_against_manifest(source, found, manifest)
     out = {}
     for n, spec in manifest.items():
+        if n not in where:
+            continue                                    # an optional tensor the checkpoint does not hold
         t = _normalise(where[n].tensor(n), spec.kind)
         out[n] = t.to(device) if device is not None else t.clone()
     for f in files:
@@ -147,4 +157,4 @@ def weights_from_tensors(tensors: Mapping[str, torch.Tensor], manifest: Mapping[
              torch.int64: "I64", torch.int16: "I16", torch.int8: "I8", torch.uint8: "U8"}
     found = {n: (tuple(t.shape), names.get(t.dtype, str(t.dtype))) for n, t in tensors.items()}
     check_against_manifest(source, found, manifest)
-    return WeightSet({n: _normalise(tensors[n], manifest[n].kind) for n in manifest}, source)
+    return WeightSet({n: _normalise(tensors[n], manifest[n].kind) for n in manifest if n in tensors}, source)
