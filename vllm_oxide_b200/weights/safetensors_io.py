@@ -118,6 +118,6 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
         f.write(hjson)
         for t in blobs:
             if t.numel():
-                f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() < (1 << 24)
-                        else memoryview(t.view(torch.uint8).reshape(-1).numpy()))
+                flat = t.reshape(-1).view(torch.uint8).numpy()      # flattened first: a tensor of no dimensions has no bytes view
+                f.write(flat.tobytes() if t.numel() < (1 << 24) else memoryview(flat))
     os.replace(tmp, path)
