@@ -801,6 +801,129 @@ def rotepel_compare(a):
     return 0
 
 
+# Layer sizes at which the Lomopel design is measured beside the Llama decoder of the same width, feed-forward,
+# layer count and attention heads: per size the attention heads (shared by the full and the windowed attention),
+# the window, and the gated delta rule's heads and sizes.
+LOMOPEL_SIZES = {
+    "1b": dict(llama="1b", width=2048, ff=8192, attn=dict(heads=32, kv_heads=8, dim=64, vdim=64), window=1024,
+               delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64)),
+    "3b": dict(llama="3b", width=3072, ff=8192, attn=dict(heads=24, kv_heads=8, dim=128, vdim=128), window=1024,
+               delta=dict(heads=24, kv_heads=12, dim=128, vdim=128, conv=4, decay_rank=96, gate_rank=96)),
+}
+
+
+def make_lomopel_engine(ls, blocks, max_seqs, tokens_per_request, context):
+    """(config, LLM): `blocks` times the four layers [attention, parallel, parallel, attention], every attention layer
+    mixing values, random weights drawn on the device."""
+    import torch
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import EngineConfig, GatedDeltaConfig, LomopelConfig, LomopelLayer, SoftmaxMixerConfig
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    at = ls["attn"]
+    full = SoftmaxMixerConfig(scale=at["dim"] ** -0.5, q_temp=(0.1, 1024), v_mix=True, **at)
+    left = SoftmaxMixerConfig(scale=1.0 / 8, window=ls["window"], rot_dims=at["dim"] // 2, rot_base=1e4, **at)
+    att = LomopelLayer("attention", attention=full, ff=ls["ff"])
+    par = LomopelLayer("parallel", left=left, right=GatedDeltaConfig(**ls["delta"]), left_scale=1.0, right_scale=1.0, ff=ls["ff"])
+    cfg = LomopelConfig(vocab=128256, width=ls["width"], layers=(att, par, par, att) * blocks, norm_eps=1e-5, embedding_scale=1.0)
+    pages_per_req = -(-(tokens_per_request + 16) // 16)
+    fields = dict(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
+                  num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=True)
+    fields.update(ENGINE_OVERRIDES)
+    tensors = random_tensors(models.lomopel_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    runner = ModelRunner(cfg, tensors, EngineConfig(**fields))
+    del tensors
+    return cfg, LLM(runner)
+
+
+def lomopel_roofline(ls, blocks, n, batch, peaks, prefill, decode):
+    """The new design's own kernels against their rooflines: algorithmic bytes (or FLOPs) of all their launches in one
+    step over the measured time, as a fraction of the measured copy bandwidth (or the measured bfloat16 product rate)."""
+    at, d, W, win = ls["attn"], ls["delta"], ls["width"], ls["window"]
+    layers = 4 * blocks
+    out = {}
+
+    def add(names, label, phase, totals, nbytes=None, flops=None):
+        ms = sum(t for op, _, t in totals if op in names)
+        if ms <= 0:
+            return
+        e = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["of_measured_hbm"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 2)
+            e["of_measured_bf16"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        out[f"{phase}:{label}"] = e
+    qd, kd, vd = at["heads"] * at["dim"], at["kv_heads"] * at["dim"], at["kv_heads"] * at["vdim"]
+    for phase, rows, totals in (("prefill", n, prefill), ("decode", batch, decode)):
+        add(("add_rmsnorm",), "add_rmsnorm", phase, totals, nbytes=(2 * layers + 1) * rows * W * (2 * 4 + 2 + 2))
+        # keys a row reads: all before it in the two full layers of a block, the window's in the two windowed ones
+        if phase == "prefill":
+            keys_full, keys_win = rows * (n + 1) / 2, sum(min(i + 1, win) for i in range(n))
+        else:
+            keys_full, keys_win = batch * (n + 3), batch * min(n + 3, win)
+        fl = 2 * blocks * (keys_full + keys_win) * at["heads"] * 2 * (at["dim"] + at["vdim"])
+        by = 2 * blocks * (keys_full + keys_win) * (kd + vd) * 2 if phase == "decode" else None
+        add(("flex_attention", "flex_attention_tc", "flex_attention_decode"), "attention", phase, totals, nbytes=by, flops=fl)
+        # q, k, v read from the projection; q written, k and v written to the cache (and the values that layers share)
+        add(("flex_prep",), "flex_prep", phase, totals, nbytes=layers * rows * (2 * qd + 2 * kd + 2 * vd) * 2)
+        seqs = 1 if phase == "prefill" else batch
+        H, K, V, G = d["heads"], d["dim"], d["vdim"], d["kv_heads"]
+        state = 2 * blocks * H * K * V * 4 * 2 * seqs
+        per_token = 2 * blocks * (2 * G * K * 4 + H * V * 2 + H * K * 4 + H * 4 + H * V * 4)
+        add(("recurrence_scan",), "recurrence_scan", phase, totals, nbytes=state + rows * per_token,
+            flops=2 * blocks * rows * 2 * H * K * V * 4)
+        C = 2 * G * K + H * V
+        add(("gated_delta_prep", "conv_state_update"), "gated_delta_prep", phase, totals,
+            nbytes=2 * blocks * rows * (C * 2 + H * K * 2 + 2 * G * K * 4 + H * V * 2 + H * K * 4 + H * 4))
+        add(("recurrence_post",), "recurrence_post", phase, totals, nbytes=2 * blocks * rows * H * V * (4 + 2 + 2))
+    return out
+
+
+def lomopel_compare(a):
+    """Prefill and decode of the Lomopel design beside the Llama decoder of the same width, feed-forward, layer count
+    and attention heads; one JSON line. Device-timed like the benchmark's own points: one step of 2,048 prompt tokens
+    (median of 5 after 3), decode steps replayed from CUDA graphs (`--steps` steps a region, median region)."""
+    import torch
+    peaks = load_peaks()
+    n, B, blocks = 2048, a.batch, 2
+    gen = a.warmup + max(a.steps, MAX_TIMED_STEPS) + 64
+    sampler = ClockSampler()
+    sampler.start()
+    points = []
+    for key in a.lomopel.split(","):
+        ls = LOMOPEL_SIZES[key]
+        point = {"sizes": key, "layers": 4 * blocks, "prompt_len": n, "batch": B}
+        for arch in ("lomopel", "llama"):
+            if arch == "lomopel":
+                cfg, llm = make_lomopel_engine(ls, blocks, B, n + gen, 8192)
+                vocab = cfg.vocab
+            else:
+                cfg, llm = make_engine(SIZES[ls["llama"]], 4 * blocks, B, n + gen, 8192)
+                vocab = cfg.vocab_size
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for _ in range(B)]
+            ms_prefill = timed_prefill(llm, prompts[0], n)
+            ms_step, ctx_tokens, launches, regions = decode_device(llm, prompts, B, a.steps, a.warmup, n, gen)
+            prefill, decode = op_profile(llm, prompts, n, B)
+            e = {"prefill_tok_s": round(n / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                 "decode_tok_s": round(B / ms_step * 1e3, 1), "decode_ms_per_step": round(ms_step, 4),
+                 "decode_hbm_frac_of_measured": round(llm.runner.step_read_bytes(int(ctx_tokens)) / ms_step / 1e6 / peaks["hbm_gbs"], 3),
+                 "launches_per_decode_step": launches // a.steps,
+                 "ops_prefill_ms": {op: round(t, 4) for op, _, t in prefill}, "ops_decode_ms": {op: round(t, 4) for op, _, t in decode}}
+            e["kernels"] = lomopel_roofline(ls, blocks, n, B, peaks, prefill, decode) if arch == "lomopel" else \
+                llama_roofline(cfg, 4 * blocks, n, B, peaks, prefill, decode)
+            point[arch] = e
+            free_engine(llm)
+            del llm
+        points.append(point)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "Lomopel beside Llama at equal width, feed-forward, layer count and attention heads: prefill and decode tok/s",
+                      "dtype": "bf16", "data": "synthetic", "peaks": peaks, "points": points, "clocks": clocks, "run": run_record()}))
+    return 0
+
+
 def main():
     if "--kernel" in sys.argv[1:]:
         return kernel_case(sys.argv[1:])
@@ -830,6 +953,9 @@ def main():
     ap.add_argument("--rotepel", default=None, metavar="SIZES", const="1b,3b", nargs="?",
                     help="instead of the benchmark's line: the Rotepel design beside Llama at equal sizes (1b, 3b or both), "
                          "prefill and decode, with the time and roofline fraction of every kernel")
+    ap.add_argument("--lomopel", default=None, metavar="SIZES", const="1b,3b", nargs="?",
+                    help="instead of the benchmark's line: the Lomopel design beside Llama at equal sizes (1b, 3b or both), "
+                         "prefill and decode, with the time and roofline fraction of every kernel")
     ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
                     help="set a field of vllm_oxide_b200.tuning.TUNING (experiments)")
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
@@ -850,6 +976,8 @@ def main():
     a.steps = max(a.steps, 1)
     if a.rotepel:
         return rotepel_compare(a)
+    if a.lomopel:
+        return lomopel_compare(a)
     prompt_len, gen_len = a.prompt_len, a.gen_len
     max_b = max(a.batch, 1 if (a.no_points or a.serve or a.timeline) else 64)
     if a.serve:

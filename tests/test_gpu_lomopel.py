@@ -28,9 +28,11 @@ def _configs():
     left_full = SM(heads=2, kv_heads=2, dim=16, vdim=16, scale=0.25, window=16, rot_dims=16, rot_base=10000.0)    # all of a head rotated
     left_one = SM(heads=3, kv_heads=3, dim=10, vdim=6, scale=0.4, window=1, rot_dims=4, rot_base=50.0)            # sees itself only
     left_wide = SM(heads=2, kv_heads=1, dim=8, vdim=24, scale=0.5, window=200)                                    # no rotation, a window never reached
-    # sizes the tensor-core attention kernels take (multiples of 16), a window that is no multiple of a tile
-    left_tc = SM(heads=6, kv_heads=2, dim=32, vdim=48, scale=0.2, window=37, rot_dims=8, rot_base=1000.0)
-    att_tc = SM(heads=4, kv_heads=1, dim=48, vdim=32, scale=0.05, q_temp=(0.3, 16), v_mix=True)
+    # keys and values of one size, 64 or 128: in bfloat16 these take the framework's tensor-core attention kernels;
+    # a window that is no multiple of a tile of keys
+    left_tc = SM(heads=6, kv_heads=2, dim=64, vdim=64, scale=0.2, window=37, rot_dims=8, rot_base=1000.0)
+    att_tc = SM(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.04, q_temp=(0.3, 16), v_mix=True)
+    att_tc128 = SM(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.03)
     right = GD(heads=4, kv_heads=2, dim=16, vdim=24, conv=3, decay_rank=5, gate_rank=6)
     right_wide = GD(heads=2, kv_heads=2, dim=40, vdim=8, conv=4, decay_rank=3, gate_rank=3)
     right_one = GD(heads=3, kv_heads=1, dim=8, vdim=12, conv=1, decay_rank=2, gate_rank=7)       # no convolution state at all
@@ -48,7 +50,7 @@ def _configs():
         # sizes that take the tensor-core kernels in bfloat16; three layers mix values
         "T": LomopelConfig(vocab=77, width=96, embedding_scale=2.0, norm_eps=1e-5, layers=(
             L("attention", attention=att_tc, ff=64), L("parallel", left=left_tc, right=right, left_scale=1.2, right_scale=0.9, ff=64),
-            L("attention", attention=att_tc, ff=0), L("attention", attention=att_tc, ff=64))),
+            L("attention", attention=att_tc, ff=0), L("attention", attention=att_tc128, ff=64))),
         "attention": LomopelConfig(vocab=50, width=48, embedding_scale=2.5, norm_eps=1e-5, layers=(L("attention", attention=att, ff=0),)),
         "parallel": LomopelConfig(vocab=50, width=48, embedding_scale=2.5, norm_eps=1e-5, layers=(par,)),
     }
@@ -186,7 +188,8 @@ def _fill(cache, tables, s, x, page):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,DV,window,sink,gate", [
     (4, 2, 24, 40, 0, True, False), (3, 3, 10, 6, 5, False, True), (8, 2, 64, 64, 40, False, True), (4, 1, 96, 48, 0, True, False),
-    (6, 2, 32, 48, 37, True, True), (2, 1, 128, 16, 1, False, False)])
+    (6, 2, 32, 48, 37, True, True), (2, 1, 128, 16, 1, False, False), (8, 2, 64, 64, 0, True, False), (4, 2, 128, 128, 0, True, True),
+    (4, 1, 128, 128, 100, False, False)])
 def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, G, D, DV, window, sink, gate):
     """Two requests in one batch over scattered pages, one with a context in the cache and a portion of
     rows, one a single decoded token far into its context. Queries and keys are made so that single
@@ -238,6 +241,7 @@ def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, 
                            sk.to(DEV) if sink else None, gd, 0.75)
     r0 = 0
     tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    wants = []
     for s in range(2):
         kk, vv = k[s].to(dtype).double(), v[s].to(dtype).double()
         qq = qd[r0:r0 + lens[s]].cpu().double().reshape(lens[s], H, D)
@@ -249,6 +253,7 @@ def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, 
         if gate:
             want = want * torch.sigmoid(gd[r0:r0 + lens[s]].cpu().double())
         assert max_rel_diff(out[r0:r0 + lens[s]].cpu(), want) < tol, s
+        wants.append(want)
         if s == 0 and window == 0:
             assert float(w[0, far_row, 3]) > 0.5         # the far key is what the row is made of
         if s == 0 and window > 1:
@@ -257,6 +262,27 @@ def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, 
             assert float(w[1].sum(-1).max()) < 1e-3      # the sink took it all
         r0 += lens[s]
     assert bool(torch.isnan(wide[:, :8]).all())
+    if dtype != torch.bfloat16 or D != DV or D not in kernels.TENSOR_CORE_HEAD_DIMS:
+        return
+    # the same rows through the tensor-core kernels, which end with the same sink, gate and factor
+    want = torch.cat(wants)
+    starts = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
+    ctxd = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
+    skd = sk.to(DEV) if sink else None
+    out.fill_(float("nan"))
+    kernels.attn_prefill_mma(qd, out, kc, vc, tables.to(DEV), starts, ctxd, 2, lens[0], H, G, D, scale, window, skd, gd, 0.75)
+    assert max_rel_diff(out.cpu(), want) < tol
+    if window == 0 and not gate:
+        plain_out = torch.full((T, H * DV), float("nan"), dtype=dtype, device=DEV)
+        kernels.attn_prefill_sm100(qd, plain_out, kc, vc, tables.to(DEV), starts, ctxd, 2, lens[0], H, G, D, scale, skd)
+        assert max_rel_diff(plain_out.cpu(), want / 0.75) < tol
+    for splits, wide_merge in ((1, False), (4, False), (8, False), (12, True)):
+        one = torch.full((1, H * DV + 8), float("nan"), dtype=dtype, device=DEV)
+        partials = torch.empty(kernels.attn_decode_partial_floats(1, G, D, splits), device=DEV) if wide_merge else None
+        arrived = torch.zeros(G, dtype=torch.int32, device=DEV) if wide_merge else None
+        kernels.attn_decode_mma(qd[T - 1:], one[:, 8:], kc, vc, tables[1:].to(DEV).contiguous(), positions[T - 1:].contiguous(), H, G, D, scale,
+                                window, splits, partials, arrived, skd, gd[T - 1:] if gate else None, 0.75)
+        assert max_rel_diff(one[:, 8:].cpu(), want[T - 1:]) < tol, splits
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -18,6 +18,10 @@
 //
 // Kernels take head_dim 64 or 128, page sizes that divide 64, G <= 16 for the decode kernel;
 // the launcher refuses anything else (the caller then uses the general kernel).
+//
+// What may follow the weighted sum (`AttnTail`, all optional): a sink per head (exp(sink) joins the
+// softmax's denominator once, a key with no value), a gate (the result times sigmoid(gate[row,
+// head * hd + d])) and a constant factor.
 #include "common.cuh"
 VOB_PDL_SWITCH(attention_mma)
 
@@ -54,6 +58,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+struct AttnTail {
+    const float* sink;                // [H], or null
+    const __nv_bfloat16* gate;        // [rows, gate_stride], or null
+    long long gate_stride;
+    float out_scale;
+};
+// The denominator of a row of `head` whose sum `L` is relative to the maximum `Ms` (base-2 scale).
+__device__ __forceinline__ float tail_den(const AttnTail& t, int head, float L, float Ms) {
+    return t.sink ? L + exp2f(t.sink[head] * 1.4426950408889634f - Ms) : L;
+}
+__device__ __forceinline__ float tail_val(const AttnTail& t, long long row, int col, float v) {
+    v *= t.out_scale;
+    if (t.gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(t.gate[row * t.gate_stride + col])));
+    return v;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -193,7 +213,8 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                         long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                         const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
-                        const int* __restrict__ context_lens, int H, int KV, int page_shift, int window, float scale_log2) {
+                        const int* __restrict__ context_lens, int H, int KV, int page_shift, int window, float scale_log2,
+                        AttnTail tail) {
     constexpr int LD = HD + 8;
     constexpr int BM = 64;
     pdl_launch_dependents();
@@ -307,11 +328,13 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
         int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
         if (rr >= total_rows) continue;
         int tok = rr / G, head = kvh * G + rr % G;
-        float inv = 1.0f / l[h];
+        float inv = 1.0f / tail_den(tail, head, l[h], m[h]);
         __nv_bfloat16* op = out + (size_t)(row0 + tok) * out_stride + (size_t)head * HD + (lane & 3) * 2;
+        const int col = head * HD + (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n)
-            *reinterpret_cast<uint32_t*>(op + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+            *reinterpret_cast<uint32_t*>(op + n * 8) = pack_bf16(tail_val(tail, row0 + tok, col + n * 8, o[n][2 * h] * inv),
+                                                                 tail_val(tail, row0 + tok, col + n * 8 + 1, o[n][2 * h + 1] * inv));
     }
 }
 
@@ -326,7 +349,7 @@ constexpr int DEC_MAX_SPLITS_WIDE = 64;
 // kernel's main path keeps its registers.
 template <int HD>
 __device__ __noinline__ void merge_partials(const float* __restrict__ all, int splits, int G, float* scratch,
-                                            __nv_bfloat16* __restrict__ out) {
+                                            __nv_bfloat16* __restrict__ out, const AttnTail& tail, int row, int head0) {
     constexpr int PART = 16 * HD + 32;
     float* ml = scratch;                                    // [splits][32]: 16 maxima, 16 sums
     float* fk = ml + DEC_MAX_SPLITS_WIDE * 32;              // [splits][16]: weight of partial k in row r
@@ -346,7 +369,7 @@ __device__ __noinline__ void merge_partials(const float* __restrict__ all, int s
             fk[k * 16 + r] = f;
             L += f * ml[k * 32 + 16 + r];
         }
-        Lrow[r] = L;
+        Lrow[r] = tail_den(tail, head0 + r, L, Ms);
     }
     __syncthreads();
     const int items = G * HD / 4, k_half = splits / 2;
@@ -365,7 +388,7 @@ __device__ __noinline__ void merge_partials(const float* __restrict__ all, int s
     __syncthreads();
     for (int e = threadIdx.x; e < G * HD; e += NTHREADS) {
         const float L = Lrow[e / HD];
-        out[e] = __float2bfloat16_rn(L > 0.f ? (hs[e] + hs[16 * HD + e]) / L : 0.f);
+        out[e] = __float2bfloat16_rn(L > 0.f ? tail_val(tail, row, head0 * HD + e, (hs[e] + hs[16 * HD + e]) / L) : 0.f);
     }
 }
 
@@ -405,7 +428,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
                        int H, int KV, int page_shift, int window, float scale_log2, float* __restrict__ partials,
-                       int* __restrict__ arrived) {
+                       int* __restrict__ arrived, AttnTail tail) {
     constexpr int LD = HD + 8;
     constexpr int PART = 16 * HD + 32;                                          // floats of one block's partial
     pdl_launch_dependents();
@@ -560,7 +583,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
             L += f * cl[w * 16 + r];
         }
         if (splits == 1) {
-            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            L = tail_den(tail, kvh * G + r, L, Ms);
+            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] =
+                __float2bfloat16_rn(L > 0.f ? tail_val(tail, seq, (kvh * G + r) * HD + d, acc / L) : 0.f);
         } else if (push) {
             // to the block that finishes this output; the row's maximum and sum to every block
             const int owner = e / chunk;
@@ -591,7 +616,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         if (!s_last) return;
         __threadfence();
         merge_partials<HD>(partials + (size_t)(seq * KV + kvh) * gridDim.z * PART, splits, G, reinterpret_cast<float*>(sK0),
-                           out + (size_t)seq * out_stride + (size_t)kvh * G * HD);
+                           out + (size_t)seq * out_stride + (size_t)kvh * G * HD, tail, seq, kvh * G);
         if (threadIdx.x == 0) arrived[seq * KV + kvh] = 0;      // ready for the next launch
     } else if (splits > 1) {
         // what was sent is there once everyone has passed this barrier
@@ -617,7 +642,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
                 acc += f * po[k];
                 L += f * pl[k];
             }
-            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            L = tail_den(tail, kvh * G + r, L, Ms);
+            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] =
+                __float2bfloat16_rn(L > 0.f ? tail_val(tail, seq, (kvh * G + r) * HD + d, acc / L) : 0.f);
         }
         // nothing of this block is read by a peer: it may leave at once
     }
@@ -649,7 +676,7 @@ int ensure_smem(Kern kernel, size_t bytes, size_t* configured) {
 template <int HD>
 int launch_prefill(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                    const int* bt, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new,
-                   int H, int KV, int page_size, int window, float scale, cudaStream_t stream) {
+                   int H, int KV, int page_size, int window, float scale, AttnTail tail, cudaStream_t stream) {
     static size_t configured = 0;
     size_t smem = prefill_smem<HD>() + (size_t)max_pages * sizeof(int);      // tiles + this request's page list
     int e = ensure_smem(attn_prefill_mma_kernel<HD>, smem, &configured);
@@ -661,13 +688,13 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
     return vob_launch(attn_prefill_mma_kernel<HD>, grid, dim3(NTHREADS), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size), window,
-        scale * 1.4426950408889634f);
+        scale * 1.4426950408889634f, tail);
 }
 
 template <int HD, int ST>
 int launch_decode_st(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                      const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                     float scale, int splits, float* partials, int* arrived, cudaStream_t stream) {
+                     float scale, int splits, float* partials, int* arrived, AttnTail tail, cudaStream_t stream) {
     static size_t configured = 0;
     // a block's page list: its share of the tiles of the longest request the block table can hold
     // (a request with few tiles uses fewer blocks, but then the tiles are few)
@@ -694,14 +721,14 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
     cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                         out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
-                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f, partials, arrived);
+                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f, partials, arrived, tail);
     return ce != cudaSuccess ? (int)ce : vob_launch_status();
 }
 
 template <int HD>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                   const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                  float scale, int splits, float* partials, int* arrived, cudaStream_t stream) {
+                  float scale, int splits, float* partials, int* arrived, AttnTail tail, cudaStream_t stream) {
     static int num_sms = 0;
     if (!num_sms) {
         int dev = 0;
@@ -714,9 +741,9 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>(H / KV, splits > 1 && !partials) + 2048));
     if (blocks <= fit3)
         return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                       window, scale, splits, partials, arrived, stream);
+                                       window, scale, splits, partials, arrived, tail, stream);
     return launch_decode_st<HD, 2>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                   window, scale, splits, partials, arrived, stream);
+                                   window, scale, splits, partials, arrived, tail, stream);
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {
@@ -735,14 +762,16 @@ VOB_EXPORT int vob_attn_mma_supported(int H, int KV, int hd, int page_size, int 
 VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                                     const void* vcache, const int* block_tables, int max_pages, const int* seq_starts,
                                     const int* context_lens, int S, int max_new, int H, int KV, int hd, int page_size,
-                                    int window, float scale, cudaStream_t stream) {
+                                    int window, float scale, const float* sink, const void* gate, long long gate_stride,
+                                    float out_scale, cudaStream_t stream) {
+    const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
     if (S <= 0 || max_new <= 0) return 0;
     if (!sizes_ok(H, KV, hd, page_size)) return VOB_ERR_UNSUPPORTED;
     if (q_stride % 8 != 0 || out_stride % 2 != 0 || S > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
     if (hd == 64) return launch_prefill<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,
-                                           context_lens, S, max_new, H, KV, page_size, window, scale, stream);
+                                           context_lens, S, max_new, H, KV, page_size, window, scale, tail, stream);
     return launch_prefill<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,
-                               context_lens, S, max_new, H, KV, page_size, window, scale, stream);
+                               context_lens, S, max_new, H, KV, page_size, window, scale, tail, stream);
 }
 
 // `splits` (1..8) blocks share each (request, kv head) as one cluster. With `partials` (float32
@@ -751,13 +780,15 @@ VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out
 VOB_EXPORT int vob_attn_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                                    const void* vcache, const int* block_tables, int max_pages, const int* positions, int S,
                                    int H, int KV, int hd, int page_size, int window, float scale, int splits,
-                                   void* partials, int* arrived, cudaStream_t stream) {
+                                   void* partials, int* arrived, const float* sink, const void* gate, long long gate_stride,
+                                   float out_scale, cudaStream_t stream) {
+    const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
     if (S <= 0) return 0;
     if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
     if ((partials == nullptr) != (arrived == nullptr)) return VOB_ERR_BAD_ARG;
     if (q_stride % 8 != 0 || splits < 1 || splits > (partials ? DEC_MAX_SPLITS_WIDE : 8) || KV > 65535) return VOB_ERR_BAD_ARG;
     if (hd == 64) return launch_decode<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
-                                          H, KV, page_size, window, scale, splits, (float*)partials, arrived, stream);
+                                          H, KV, page_size, window, scale, splits, (float*)partials, arrived, tail, stream);
     return launch_decode<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
-                              page_size, window, scale, splits, (float*)partials, arrived, stream);
+                              page_size, window, scale, splits, (float*)partials, arrived, tail, stream);
 }

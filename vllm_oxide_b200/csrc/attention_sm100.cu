@@ -91,7 +91,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                           const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long long out_stride,
                           const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                           const int* __restrict__ context_lens, int H, int KV, int page_shift, int num_pages,
-                          float scale_log2, int* __restrict__ err_flag) {
+                          float scale_log2, int* __restrict__ err_flag, const float* __restrict__ sink) {
     static_assert(HD == 64 || HD == 128, "rows of one or two 128-byte swizzle spans");
     constexpr int ST = stages<HD>();
     constexpr int NH = HD / 64;                    // 64-wide halves of the head dimension, each a tile of 128-byte rows
@@ -386,6 +386,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         }
         if (ok && wait_all(kv_free + (n_tiles - 1) % ST, ((n_tiles - 1) / ST) & 1, 21)) {
             tcgen05_fence_after();
+            // a sink: exp(sink[head]) joins the denominator once (l and O are relative to m_ref, in the base-2 scale)
+            if (sink && row_valid) l += exp2f(sink[kvh * G + rr % G] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.f : m_ref));
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst = out + (size_t)(row0 + rr / G) * out_stride + (size_t)(kvh * G + rr % G) * HD;
 #pragma unroll
@@ -466,11 +468,13 @@ VOB_EXPORT int vob_attn_prefill_sm100_supported(int H, int KV, int hd, int page_
 
 // q [q_rows, H*hd] (row stride q_stride elements), out likewise; kcache / vcache [num_pages, KV,
 // page_size, hd]; block_tables int32 [S, max_pages]; seq_starts int32 [S+1]; context_lens int32 [S];
-// max_new = the longest portion of the step.
+// max_new = the longest portion of the step. `sink` (float32 [H], may be null): exp(sink[head]) is added to every
+// row's softmax denominator, a key with no value.
 VOB_EXPORT int vob_attn_prefill_sm100(const void* q, long long q_rows, long long q_stride, void* out, long long out_stride,
                                       const void* kcache, const void* vcache, long long num_pages, const int* block_tables,
                                       int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new, int H,
-                                      int KV, int hd, int page_size, float scale, int* err_flag, cudaStream_t stream) {
+                                      int KV, int hd, int page_size, float scale, int* err_flag, const float* sink,
+                                      cudaStream_t stream) {
     if (S <= 0 || max_new <= 0) return 0;
     if (!vob_attn_prefill_sm100_supported(H, KV, hd, page_size, max_pages)) return VOB_ERR_UNSUPPORTED;
     if (!(scale > 0.f) || q_rows <= 0 || num_pages <= 0 || num_pages > 0x7fffffff) return VOB_ERR_BAD_ARG;
@@ -509,7 +513,7 @@ VOB_EXPORT int vob_attn_prefill_sm100(const void* q, long long q_rows, long long
         }
         return vob_launch(attn_prefill_sm100_kernel<64>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                           out_stride, block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size),
-                          (int)num_pages, scale * 1.4426950408889634f, err_flag);
+                          (int)num_pages, scale * 1.4426950408889634f, err_flag, sink);
     }
     static size_t configured = 0;
     size_t smem = fixed_smem<128>() + (size_t)max_pages * sizeof(int);
@@ -520,5 +524,5 @@ VOB_EXPORT int vob_attn_prefill_sm100(const void* q, long long q_rows, long long
     }
     return vob_launch(attn_prefill_sm100_kernel<128>, grid, dim3(NTHREADS), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                       out_stride, block_tables, max_pages, seq_starts, context_lens, H, KV, log2_exact(page_size),
-                      (int)num_pages, scale * 1.4426950408889634f, err_flag);
+                      (int)num_pages, scale * 1.4426950408889634f, err_flag, sink);
 }

@@ -1196,6 +1196,18 @@ def attn_mma_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_si
     return bool(f(num_heads, num_kv_heads, head_dim, page_size, int(decode)))
 
 
+def _attn_tail(op, q, sink, gate, num_heads, out_scale):
+    """Checked arguments of what may follow the weighted sum: a sink per head (float32 [H]), a gate ([T, H * hd] bfloat16,
+    any row stride: the result times its sigmoid) and a constant factor."""
+    _cuda(op, q, sink, gate)
+    _f32_vec(sink, num_heads, op, "sink")
+    if gate is not None:
+        _rows_2d(gate, op, "gate")
+        if gate.shape != q.shape or gate.dtype != torch.bfloat16:
+            raise ShapeError(op, f"gate must be bfloat16 {list(q.shape)}, got {gate.dtype} {list(gate.shape)}")
+    return _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale)
+
+
 def _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim):
     _cuda(op, q, out, kcache, vcache, block_tables)
     _rows_2d(q, op, "q")
@@ -1220,10 +1232,11 @@ def _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num
 
 @_timed
 def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
-                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0, sink=None, gate=None,
+                     out_scale: float = 1.0) -> None:
     """Tensor-core attention for portions of prompts and mixed batches (bfloat16). q/out [T, H*hd];
     seq_starts int32 [S+1] (first row of each request), context_lens int32 [S] (keys cached before
-    the step), max_new = the longest portion."""
+    the step), max_new = the longest portion. `sink`, `gate`, `out_scale`: see `_attn_tail`."""
     op = "attn_prefill_mma"
     if not scale > 0:
         raise ShapeError(op, f"the score scale must be positive, got {scale}")
@@ -1233,11 +1246,12 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
     _int32_vec(context_lens, num_seqs, op, "context_lens")
     if block_tables.shape[0] < num_seqs:
         raise ShapeError(op, f"block_tables has {block_tables.shape[0]} rows for {num_seqs} requests")
+    tail = _attn_tail(op, q, sink, gate, num_heads, out_scale)
     f = _fn("attention_mma", "vob_attn_prefill_mma",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P])
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _L, _F, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
              block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
-             head_dim, kcache.shape[2], int(window), float(scale), _stream()), op)
+             head_dim, kcache.shape[2], int(window), float(scale), *tail, _stream()), op)
 
 
 def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:
@@ -1250,8 +1264,9 @@ def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: in
 
 @_timed
 def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
-                       num_heads: int, num_kv_heads: int, head_dim: int, scale: float) -> None:
-    """Attention for portions of prompts and mixed batches on the tcgen05 tensor cores (bfloat16,
+                       num_heads: int, num_kv_heads: int, head_dim: int, scale: float, sink=None) -> None:
+    """`sink` (float32 [H], optional): exp(sink[head]) joins every row's softmax denominator, a key with no value.
+    Attention for portions of prompts and mixed batches on the tcgen05 tensor cores (bfloat16,
     head_dim 64 or 128, no window): Q, K and V tiles by TMA straight from the pages of the cache, scores
     and output in tensor memory. Arguments as `attn_prefill_mma`."""
     op = "attn_prefill_sm100"
@@ -1282,17 +1297,21 @@ def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context
                              "heads per kv head, page size a power of two from 8 to 128)")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(context_lens, num_seqs, op, "context_lens")
+    _cuda(op, q, sink)
+    _f32_vec(sink, num_heads, op, "sink")
     f = _fn("attention_sm100", "vob_attn_prefill_sm100",
-            [_P, _L, _L, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P])
+            [_P, _L, _L, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P])
     _check(f(_ptr(q), q.shape[0], q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
              _ptr(block_tables), block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads,
-             num_kv_heads, head_dim, kcache.shape[2], float(scale), _ptr(_scratch_for(q.device).err), _stream()), op)
+             num_kv_heads, head_dim, kcache.shape[2], float(scale), _ptr(_scratch_for(q.device).err), _ptr(sink), _stream()), op)
 
 
 @_timed
 def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int = 0, splits: int = 1, partials=None, arrived=None) -> None:
-    """Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
+                    scale: float, window: int = 0, splits: int = 1, partials=None, arrived=None, sink=None, gate=None,
+                    out_scale: float = 1.0) -> None:
+    """`sink`, `gate`, `out_scale`: see `_attn_tail`.
+    Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
     With splits > 1 (at most 8) each request's keys are shared out over the blocks of a cluster,
     which merge their partial results through distributed shared memory. With `partials` (float32,
     `attn_decode_partial_floats` elements) and `arrived` (int32 zeros, one per request and kv head;
@@ -1321,11 +1340,12 @@ def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: 
             raise ShapeError(op, f"partials must be contiguous float32, 16-byte aligned, with at least {need} elements")
         if arrived.dtype != torch.int32 or not arrived.is_contiguous() or arrived.numel() < S * num_kv_heads:
             raise ShapeError(op, f"arrived must be contiguous int32 with at least {S * num_kv_heads} elements")
+    tail = _attn_tail(op, q, sink, gate, num_heads, out_scale)
     f = _fn("attention_mma", "vob_attn_decode_mma",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P])
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _P, _L, _F, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
              block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
-             float(scale), int(splits), _ptr(partials), _ptr(arrived), _stream()), op)
+             float(scale), int(splits), _ptr(partials), _ptr(arrived), *tail, _stream()), op)
 
 
 def attn_decode_partial_floats(num_seqs: int, num_kv_heads: int, head_dim: int, splits: int) -> int:

@@ -28,6 +28,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import kernels
+from .attention import decode_split_rule
 from .base import CacheSpec, LayerCache, Mixer, PagedTensorSpec, StepContext, aligned
 from .linear import to_compute
 from .rotary import rotary_inv_freq
@@ -94,6 +95,10 @@ class SoftmaxAttention(Mixer):
         self.mix_weight = mix_weight.to(**f32).reshape(1).contiguous() if self.v_mode == 2 else None
         self.shared_name = shared_name
         self.hidden, self.dtype = hidden, dtype
+        self.impl = "auto"            # "general" forces the general kernel (tests)
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self._partials = None         # scratch of the decode kernel's merge through global memory, made at first need
+        self._arrived = None
 
     # ------------------------------------------------------------------ what the runtime asks
     def cache_spec(self) -> Optional[CacheSpec]:
@@ -114,8 +119,17 @@ class SoftmaxAttention(Mixer):
         es = self.w_in.element_size()
         return aligned(rows * self.w_in.shape[0] * es) + aligned(rows * self.n_pre * es) + self.core_workspace_bytes(rows)
 
+    def tensor_core_sizes(self) -> bool:
+        """Keys and values of one size that the framework's tensor-core attention kernels are built for."""
+        return self.D == self.DV and self.D in kernels.TENSOR_CORE_HEAD_DIMS and self.H // self.G <= 16
+
     def kernel_modules(self, dtype, max_rows):
-        return ("gemm_f32", "attention_flex") if dtype == torch.float32 else ("gemm_sm100", "attention_flex")
+        if dtype == torch.float32:
+            return ("gemm_f32", "attention_flex")
+        mods = ["gemm_sm100", "attention_flex"]
+        if self.tensor_core_sizes():
+            mods += ["attention_mma"] + ([] if self.window or self.gated else ["attention_sm100"])
+        return tuple(mods)
 
     # ------------------------------------------------------------------ the step
     def core(self, proj: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state, pre_out: torch.Tensor,
@@ -133,8 +147,47 @@ class SoftmaxAttention(Mixer):
                           self.inv_freq, self.rot, self.unit_rms, self.eps, self.q_temp, self.mix_weight, v_first, self.v_mode, q, kc, vc,
                           self.H, self.G, self.D, self.DV)
         gate = proj[:, self.g_off:self.g_off + self.n_pre] if self.gated else None
-        kernels.flex_attention(q, pre_out, kc, vc, ctx.block_tables[cache.group], ctx.row_seq, ctx.positions, self.H, self.G, self.D,
-                               self.DV, self.scale, self.window, self.sink, gate, out_scale)
+        self.attend(q, pre_out, ctx, cache, gate, out_scale)
+
+    def attend(self, q, out, ctx: StepContext, cache: LayerCache, gate, out_scale: float) -> None:
+        """bfloat16 with keys and values of one size the framework's tensor-core kernels take (64 or 128): steps of
+        single tokens go to the split-key decode kernel, portions to the tcgen05 kernel (no window, no gate) or the
+        mma.sync one, each of which ends with this mixer's sink, gate and factor; a mixed step's leading single tokens
+        go to the decode kernel and the portions behind them to the portion kernel. Everything else (float32, other
+        sizes) goes to the general kernel."""
+        kc, vc = cache.tensors[0], cache.tensors[1]
+        page, bt = kc.shape[2], ctx.block_tables[cache.group]
+        H, G, D = self.H, self.G, self.D
+        if (self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0 and self.tensor_core_sizes()
+                and kernels.attn_mma_supported(H, G, D, page, True) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+            if ctx.decode_only:
+                self._attend_single(q, out, ctx, cache, bt, ctx.rows, gate, out_scale)
+                return
+            if ctx.max_new > 0:
+                lead = ctx.lead_single if 0 < ctx.lead_single < ctx.seqs else 0
+                if lead:
+                    self._attend_single(q, out, ctx, cache, bt, lead, gate, out_scale)
+                if (self.window == 0 and gate is None and out_scale == 1.0 and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0
+                        and kernels.attn_prefill_sm100_supported(H, G, D, page, bt.shape[1])):
+                    kernels.attn_prefill_sm100(q, out, kc, vc, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:], ctx.seqs - lead,
+                                               ctx.max_new, H, G, D, self.scale, self.sink)
+                else:
+                    kernels.attn_prefill_mma(q, out, kc, vc, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:], ctx.seqs - lead,
+                                             ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
+                return
+        kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
+                               gate, out_scale)
+
+    def _attend_single(self, q, out, ctx: StepContext, cache: LayerCache, bt, count: int, gate, out_scale: float) -> None:
+        """The decode kernel on the first `count` rows, row i belonging to request i."""
+        splits, wide = decode_split_rule(count, self.G, self.num_sms, ctx.long_context and not self.window)
+        if wide and self._partials is None:
+            floats = kernels.attn_decode_partial_floats(1, 1, self.D, 3 * self.num_sms)    # requests x kv heads x splits <= 3 SMs
+            self._partials = torch.empty(floats, dtype=torch.float32, device=q.device)
+            self._arrived = torch.zeros(self.num_sms, dtype=torch.int32, device=q.device)
+        kernels.attn_decode_mma(q[:count], out[:count], cache.tensors[0], cache.tensors[1], bt, ctx.positions[:count], self.H, self.G,
+                                self.D, self.scale, self.window, splits, self._partials if wide else None,
+                                self._arrived if wide else None, self.sink, gate[:count] if gate is not None else None, out_scale)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
         T = x.shape[0]
