@@ -865,7 +865,7 @@ def lomopel_roofline(ls, blocks, n, batch, peaks, prefill, decode):
             keys_full, keys_win = batch * (n + 3), batch * min(n + 3, win)
         fl = 2 * blocks * (keys_full + keys_win) * at["heads"] * 2 * (at["dim"] + at["vdim"])
         by = 2 * blocks * (keys_full + keys_win) * (kd + vd) * 2 if phase == "decode" else None
-        add(("flex_attention", "flex_attention_tc", "flex_attention_decode"), "attention", phase, totals, nbytes=by, flops=fl)
+        add(("flex_attention", "attn_prefill_sm100", "attn_prefill_mma", "attn_decode_mma"), "attention", phase, totals, nbytes=by, flops=fl)
         # q, k, v read from the projection; q written, k and v written to the cache (and the values that layers share)
         add(("flex_prep",), "flex_prep", phase, totals, nbytes=layers * rows * (2 * qd + 2 * kd + 2 * vd) * 2)
         seqs = 1 if phase == "prefill" else batch

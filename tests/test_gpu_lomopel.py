@@ -163,6 +163,24 @@ def test_scaled_embedding_scaled_add_and_gelu_gate():
     assert max_rel_diff(out16, a.bfloat16().double() @ w.bfloat16().double().T + b.bfloat16().double()) < 1e-2
 
 
+@pytest.mark.parametrize("rows", [8, 40, 700])
+def test_products_whose_epilogue_applies_the_gelu_gate(rows):
+    """Few rows: the one-SM tcgen05 product; many: the two-SM one. Both against gate and up done plainly."""
+    from vllm_oxide_b200 import kernels
+    torch.manual_seed(2)
+    K, I = 96, 136
+    x = (torch.randn(rows, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.3).bfloat16()
+    want = plain.gelu_tanh(x.double() @ w[:I].double().T) * (x.double() @ w[I:].double().T)
+    out = torch.empty(rows, I, dtype=torch.bfloat16, device=DEV)
+    if rows <= kernels.FUSED_GEMM_MAX_ROWS:
+        kernels.gemm_swiglu(x, w, out, activation="gelu_tanh")
+    else:
+        kernels.gemm_pair_swiglu(x, w, out, "gelu_tanh")
+    kernels.gemm_sm100_check()
+    assert max_rel_diff(out, want) < 1e-2
+
+
 # ------------------------------------------------------------------------------------ attention kernels
 def _paged(total, page, heads_widths, dtype, spare=3):
     """Block tables over scattered pages for requests of `total` tokens; cache tensors full of NaN."""
@@ -391,9 +409,12 @@ def test_gated_delta_kernels_portions_state_and_shared_heads(dtype, H, G, K, V, 
             decay, beta, o = torch.empty(T, H * K, device=DEV), torch.empty(T, H, device=DEV), torch.empty(T, H * V, device=DEV)
             kernels.gated_delta_prep(rows, 0, C, lows, 4, cw.to(DEV), cstate, a_log.to(DEV), dt_bias.to(DEV), pos, rs, starts, sl, len(step),
                                      H, G, K, V, q, k, v, decay, beta)
-            if cstate is not None:
+            # the convolution state is moved on by a kernel of its own, or by the scan on its way
+            if cstate is not None and slots == (2, 0):
                 kernels.conv_state_update(rows, 0, cstate, starts, sl, len(step))
-            kernels.recurrence_scan(2, q, k, v, decay, beta, None, state, starts, sl, len(step), H, o, rk_heads=G)
+            kernels.recurrence_scan(2, q, k, v, decay, beta, None, state, starts, sl, len(step), H, o, rk_heads=G,
+                                    conv_x=rows[:, :C] if cstate is not None and slots != (2, 0) else None,
+                                    conv_state=cstate if slots != (2, 0) else None)
             r = 0
             for s, c in step:
                 got[s].append(o[r:r + c].cpu())

@@ -16,8 +16,11 @@
 VOB_PDL_SWITCH(attention_flex)
 
 // ---------------------------------------------------------------------------------------------
-// Preparation. One block of 128 threads per token; a warp takes one head at a time (q heads, then k
-// heads, then v heads), lane l holding features l, l + 32, ... (heads up to 256 wide).
+// Preparation. Grid (tokens, ceil((H + 2 G) / 8)), blocks of 256 threads: a warp takes one head of one token
+// (q heads, then k heads, then v heads), lane l holding features l, l + 32, ... (heads up to 256 wide); a
+// head is a short chain of loads, a reduction and stores, so many independent warps are what hides it, and
+// the head's features are asked for before the token's position and slot are known (padding rows are rows of
+// the projection like any other).
 //   q, k:  the first `rot` features of a head are rotated, feature i with i + rot / 2, by
 //          float(pos) * inv_freq[i]; then (unit_rms) the head is divided by sqrt(mean(x^2) + eps);
 //          q is also multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0).
@@ -25,8 +28,9 @@ VOB_PDL_SWITCH(attention_flex)
 //          v_mode 2: v <- (1 - lambda) v + lambda v_first, lambda = *vmix.
 // Rows with a negative position (padding) are left alone; a negative slot skips the cache write.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(128)
+// NI: features a lane holds of a q or k head, 32 * NI >= D.
+template <typename T, int NI>
+__global__ void __launch_bounds__(256)
 flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const int* __restrict__ positions,
                  const int* __restrict__ slots, const float* __restrict__ inv_freq, int rot, int unit_rms, float eps,
                  float temp_coef, int temp_every, const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode,
@@ -36,35 +40,35 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
     pdl_wait(61);
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[t];
-    if (pos < 0) return;
     const int slot = slots ? slots[t] : -1;
     const T* row = proj + (size_t)t * ld;
     const int half = rot >> 1;
-    const float fpos = (float)pos;
-    for (int job = warp; job < H + 2 * G; job += 4) {
+    {
+        const int job = blockIdx.y * 8 + warp;
+        if (job >= H + 2 * G) return;
         if (job < H + G) {
             const bool is_q = job < H;
             const int head = is_q ? job : job - H;
             const T* src = row + (is_q ? q_off : k_off) + (size_t)head * D;
-            float x[8];
+            float x[NI], y[NI];                      // a feature and, where it is rotated, its partner
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int f = lane + 32 * i;
+                x[i] = f < D ? ld_f(src + f) : 0.f;
+                y[i] = f < rot ? ld_f(src + (f < half ? f + half : f - half)) : 0.f;
+            }
+            if (pos < 0) return;
+            const float fpos = (float)pos;
             float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
-                float v = 0.f;
-                if (f < D) {
-                    if (f < rot) {
-                        const int idx = f < half ? f : f - half;
-                        const float ang = fpos * inv_freq[idx];
-                        const float cs = cosf(ang), sn = sinf(ang);
-                        const float a = ld_f(src + idx), b = ld_f(src + idx + half);
-                        v = f < half ? a * cs - b * sn : b * cs + a * sn;
-                    } else {
-                        v = ld_f(src + f);
-                    }
+                if (f < rot) {
+                    float sn, cs;
+                    sincosf(fpos * inv_freq[f < half ? f : f - half], &sn, &cs);
+                    x[i] = f < half ? x[i] * cs - y[i] * sn : x[i] * cs + y[i] * sn;
                 }
-                x[i] = v;
-                ss = fmaf(v, v, ss);
+                ss = fmaf(x[i], x[i], ss);
             }
             float mul = 1.f;
             if (unit_rms) mul = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
@@ -73,15 +77,16 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
             if (is_q) {
                 dst = q_out + (size_t)t * ld_q + (size_t)head * D;
             } else {
-                if (slot < 0) continue;
+                if (slot < 0) return;
                 dst = kcache + ((size_t)((slot / page_size) * G + head) * page_size + slot % page_size) * D;
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
                 if (f < D) st_f(dst + f, x[i] * mul);
             }
         } else {
+            if (pos < 0) return;
             const int head = job - H - G;
             const T* src = row + v_off + (size_t)head * DV;
             T* vf = v_first ? v_first + ((size_t)t * G + head) * DV : nullptr;
@@ -107,10 +112,17 @@ VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int
     if (rot > 0 && !inv_freq) return VOB_ERR_BAD_ARG;
     if ((v_mode == 1 || v_mode == 2) && !v_first) return VOB_ERR_BAD_ARG;
     if (v_mode == 2 && !vmix) return VOB_ERR_BAD_ARG;
-    VOB_DISPATCH_ELEM(code, return vob_launch(flex_prep_kernel<ElemT>, dim3(T), dim3(128), 0, stream, (const ElemT*)proj, ld, q_off,
-                                              k_off, v_off, positions, slots, inv_freq, rot, unit_rms, eps, temp_coef, temp_every, vmix,
-                                              (ElemT*)v_first, v_mode, (ElemT*)q_out, ld_q, (ElemT*)kcache, (ElemT*)vcache, H, G, D, DV,
-                                              page_size));
+    if ((H + 2 * G + 7) / 8 > 65535) return VOB_ERR_UNSUPPORTED;
+#define VOB_PREP(NI_)                                                                                                                  \
+    VOB_DISPATCH_ELEM(code, return vob_launch(flex_prep_kernel<ElemT, NI_>, dim3(T, (H + 2 * G + 7) / 8), dim3(256), 0, stream,              \
+                                              (const ElemT*)proj, ld, q_off, k_off, v_off, positions, slots, inv_freq, rot, unit_rms, eps,  \
+                                              temp_coef, temp_every, vmix, (ElemT*)v_first, v_mode, (ElemT*)q_out, ld_q, (ElemT*)kcache,   \
+                                              (ElemT*)vcache, H, G, D, DV, page_size))
+    if (D <= 32) VOB_PREP(1);
+    else if (D <= 64) VOB_PREP(2);
+    else if (D <= 128) VOB_PREP(4);
+    else VOB_PREP(8);
+#undef VOB_PREP
     return 0;
 }
 

@@ -121,7 +121,7 @@ struct EpiArgs {
     int q_dim, kv_dim, hd, KV, page_size;
     int ssq_tiles, ld_ssq;
     float inv_h, eps;
-    int pad_;
+    int act;                           // EPI_SWIGLU: the gate's activation, 0 silu, 1 the tanh form of gelu
     // EPI_PICK
     const float* temperature;          // [T] or null (greedy)
     const uint32_t* seeds;             // [T][2]
@@ -569,7 +569,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (fo < N) {
                     for (int k = col / (BM / 2); k < nk; k += 2) {
                         const float g = fin[k * BM + c], u = fin[k * BM + c + BM / 2];
-                        store_out<OutT>(C + (size_t)(t0 + tok_first + k * splits) * ldc + fo, g / (1.0f + expf(-g)) * u);
+                        const float a = qa.act == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                                    : g / (1.0f + expf(-g));
+                        store_out<OutT>(C + (size_t)(t0 + tok_first + k * splits) * ldc + fo, a * u);
                     }
                 }
             } else if (EPI == EPI_QKV) {
@@ -1043,6 +1045,15 @@ VOB_EXPORT int vob_gemm_sm100_ex(const void* X, long long ldx, const void* W, lo
 VOB_EXPORT int vob_gemm_sm100_swiglu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int T,
                                      int I, int K, int splits, int* err_flag, cudaStream_t stream) {
     EpiArgs ea = {};
+    return vob_gemm_sm100_ex(X, ldx, W, ldw, C, ldc, VOB_BF16, T, I, K, splits, EPI_SWIGLU, &ea, err_flag, stream);
+}
+
+// The same with the gate's activation chosen: act 0 silu, 1 the tanh form of gelu.
+VOB_EXPORT int vob_gemm_sm100_glu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc, int T,
+                                  int I, int K, int splits, int act, int* err_flag, cudaStream_t stream) {
+    if (act != 0 && act != 1) return VOB_ERR_BAD_ARG;
+    EpiArgs ea = {};
+    ea.act = act;
     return vob_gemm_sm100_ex(X, ldx, W, ldw, C, ldc, VOB_BF16, T, I, K, splits, EPI_SWIGLU, &ea, err_flag, stream);
 }
 

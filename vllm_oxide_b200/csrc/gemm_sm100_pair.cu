@@ -79,7 +79,8 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
 // gate / up activations ever going to memory. N counts output features in both modes.
 enum { PAIR_STORE = 0, PAIR_SWIGLU = 1 };
 
-template <typename OutT, int EPI>
+// ACT (PAIR_SWIGLU only): the gate's activation, 0 silu, 1 the tanh form of gelu.
+template <typename OutT, int EPI, int ACT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        OutT* __restrict__ C, long long ldc, int T, int N, int K, int wide, int* __restrict__ err_flag) {
@@ -267,10 +268,18 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                         // the last place of float32, far inside the bfloat16 rounding of the result): the
                         // precise expf and division made this epilogue longer than the tile's products
                         // (measured: 133-187 us per call against 94 us for the products alone)
-                        float e, rcp;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-g * 1.4426950408889634f));
-                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
-                        const float y = g * rcp * u;
+                        float y;
+                        if (ACT == 1) {
+                            // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u, the tanh by the special-function unit too
+                            float th;
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * fmaf(0.044715f * g * g, g, g)));
+                            y = 0.5f * g * (1.0f + th) * u;
+                        } else {
+                            float e, rcp;
+                            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-g * 1.4426950408889634f));
+                            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
+                            y = g * rcp * u;
+                        }
                         if (wide) sb[tok * FEATS + fl] = __float2bfloat16_rn(y);
                         else if (t0 + c + tok < T && fbase + fl < N) store_out<OutT>(C + (size_t)(t0 + c + tok) * ldc + fbase + fl, y);
                     }
@@ -338,14 +347,14 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, 
 
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + 2 * EPI_GROUP_BYTES;     // tiles, alignment slack, barriers, epilogue buffers
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, int ACT = 0>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc, int T, int N, int K, int* err_flag, cudaStream_t stream) {
     // 16-byte stores of C need aligned rows and a feature count that no piece of 8 straddles
     const int wide = (ldc % 8 == 0 && ((uintptr_t)C & 15) == 0 && N % 8 == 0) ? 1 : 0;
     static bool configured = false;
     static int num_sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<OutT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<OutT, EPI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         cudaGetDevice(&dev);
@@ -371,7 +380,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, long long ldc,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_pair_kernel<OutT, EPI>, mw, mx, (OutT*)C, ldc, T, N, K, wide, err_flag);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_pair_kernel<OutT, EPI, ACT>, mw, mx, (OutT*)C, ldc, T, N, K, wide, err_flag);
     return e != cudaSuccess ? (int)e : vob_launch_status();
 }
 
@@ -405,4 +414,20 @@ VOB_EXPORT int vob_gemm_sm100_pair_swiglu(const void* X, long long ldx, const vo
     e = make_map(&mx, X, T, K, ldx, BTH);
     if (e) return e;
     return launch<__nv_bfloat16, PAIR_SWIGLU>(mw, mx, C, ldc, T, I, K, err_flag, stream);
+}
+
+// The same with the gate's activation chosen: act 0 silu, 1 the tanh form of gelu.
+VOB_EXPORT int vob_gemm_sm100_pair_glu(const void* X, long long ldx, const void* W, long long ldw, void* C, long long ldc,
+                                       int T, int I, int K, int act, int* err_flag, cudaStream_t stream) {
+    if (act == 0) return vob_gemm_sm100_pair_swiglu(X, ldx, W, ldw, C, ldc, T, I, K, err_flag, stream);
+    if (act != 1) return VOB_ERR_BAD_ARG;
+    if (T <= 0 || I <= 0) return 0;
+    if (K <= 0 || ldx < K || ldw < K || ldc < I) return VOB_ERR_BAD_ARG;
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)X % 16) != 0 || ((uintptr_t)W % 16) != 0) return VOB_ERR_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int e = make_map(&mw, W, 2LL * I, K, ldw, BMH / 2);
+    if (e) return e;
+    e = make_map(&mx, X, T, K, ldx, BTH);
+    if (e) return e;
+    return launch<__nv_bfloat16, PAIR_SWIGLU, 1>(mw, mx, C, ldc, T, I, K, err_flag, stream);
 }

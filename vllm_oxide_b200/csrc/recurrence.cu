@@ -125,10 +125,11 @@ VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, in
 //   strength[h] = sigmoid(proj[b_off + h])
 //   decay[h, c] = exp(-exp(a_log[h]) * softplus(low[a_off + h K + c] + dt_bias[h K + c]))
 // `low` [T, ld_low] is the output of the second, low-rank projections. Rows with a negative position
-// (padding) are skipped. Launch: one block of 128 threads per token; a warp takes one head (or one
-// head's decays, or the strengths) at a time. K up to 512.
+// (padding) are skipped. Launch: grid (tokens, ceil(jobs / 4)), blocks of 128 threads; a warp takes one
+// head (or one head's decays, or the strengths) of one token. K up to 512.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+// NI: key channels a lane holds of a q or k head, 32 * NI >= K.
+template <typename T, int NI>
 __global__ void __launch_bounds__(128)
 gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_off, const T* __restrict__ low, long ld_low, int a_off,
                         const float* __restrict__ cw, int taps, const float* __restrict__ cstate, const float* __restrict__ a_log,
@@ -154,15 +155,17 @@ gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_of
         return y / (1.0f + expf(-y));
     };
     const int jobs = 2 * G + 2 * H + 1;
-    for (int job = warp; job < jobs; job += 4) {
+    {
+        const int job = blockIdx.y * 4 + warp;
+        if (job >= jobs) return;
         if (job < 2 * G) {                           // a q or k head: convolution, silu, unit length
             const bool is_q = job < G;
             const int head = is_q ? job : job - G;
             const int c0 = job * K;                  // q heads then k heads lie side by side
-            float x[16];
+            float x[NI];
             float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
                 x[i] = f < K ? conv_silu(c0 + f) : 0.f;
                 ss = fmaf(x[i], x[i], ss);
@@ -171,7 +174,7 @@ gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_of
             if (is_q) mul *= 1.0f / sqrtf((float)K);
             float* dst = (is_q ? q_out : k_out) + (size_t)t * G * K + (size_t)head * K;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
                 if (f < K) dst[f] = x[i] * mul;
             }
@@ -203,9 +206,18 @@ VOB_EXPORT int vob_gated_delta_prep(const void* proj, int code, long ld, int x_o
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || K <= 0 || V <= 0 || taps < 1 || H % G != 0) return VOB_ERR_BAD_ARG;
     if (K > 512) return VOB_ERR_UNSUPPORTED;
-    VOB_DISPATCH_ELEM(code, return vob_launch(gated_delta_prep_kernel<ElemT>, dim3(T), dim3(128), 0, stream, (const ElemT*)proj, ld, x_off,
-                                              b_off, (const ElemT*)low, ld_low, a_off, cw, taps, cstate, a_log, dt_bias, positions, row_seq,
-                                              seq_starts, state_slots, H, G, K, V, q_out, k_out, (ElemT*)v_out, decay, strength));
+    if ((2 * G + 2 * H + 1 + 3) / 4 > 65535) return VOB_ERR_UNSUPPORTED;
+#define VOB_GDPREP(NI_)                                                                                                              \
+    VOB_DISPATCH_ELEM(code, return vob_launch(gated_delta_prep_kernel<ElemT, NI_>, dim3(T, (2 * G + 2 * H + 1 + 3) / 4), dim3(128), 0,       \
+                                              stream, (const ElemT*)proj, ld, x_off, b_off, (const ElemT*)low, ld_low, a_off, cw, taps,     \
+                                              cstate, a_log, dt_bias, positions, row_seq, seq_starts, state_slots, H, G, K, V, q_out, k_out, \
+                                              (ElemT*)v_out, decay, strength))
+    if (K <= 32) VOB_GDPREP(1);
+    else if (K <= 64) VOB_GDPREP(2);
+    else if (K <= 128) VOB_GDPREP(4);
+    else if (K <= 256) VOB_GDPREP(8);
+    else VOB_GDPREP(16);
+#undef VOB_GDPREP
     return 0;
 }
 
@@ -214,8 +226,18 @@ VOB_EXPORT int vob_gated_delta_prep(const void* proj, int code, long ld, int x_o
 // first. A request that brought n rows keeps its own last entries where n < taps - 1:
 //   new[m] = x_(n - (taps - 1) + m) if that row is of this step, else old[m + n],   m = 0 .. taps - 2
 // (in place, m ascending: old[m + n] lies behind what has been written). Runs behind the kernel
-// that read the old state. Launch: grid (requests, ceil(C / 128)).
+// that read the old state. Launch: grid (requests, ceil(C / 128)). The scan in mode 2 can do the same
+// on its way (`conv_x` given): its blocks of a request share the channels out among themselves.
 // ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void conv_state_shift(const T* __restrict__ x, long ld, int C, int taps, float* __restrict__ st, int r0, int n,
+                                                 int c) {
+    for (int m = 0; m < taps - 1; ++m) {
+        const int tau = n - (taps - 1) + m;
+        st[(size_t)m * C + c] = tau >= 0 ? ld_f(x + (size_t)(r0 + tau) * ld + c) : st[(size_t)(m + n) * C + c];
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 conv_state_update_kernel(const T* __restrict__ proj, long ld, int x_off, int C, int taps, float* __restrict__ cstate,
@@ -225,11 +247,7 @@ conv_state_update_kernel(const T* __restrict__ proj, long ld, int x_off, int C, 
     const int s = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
     const int r0 = seq_starts[s], n = seq_starts[s + 1] - r0;
     if (n <= 0 || c >= C) return;
-    float* st = cstate + (size_t)state_slots[s] * (taps - 1) * C;
-    for (int m = 0; m < taps - 1; ++m) {
-        const int tau = n - (taps - 1) + m;
-        st[(size_t)m * C + c] = tau >= 0 ? ld_f(proj + (size_t)(r0 + tau) * ld + x_off + c) : st[(size_t)(m + n) * C + c];
-    }
+    conv_state_shift(proj + x_off, ld, C, taps, cstate + (size_t)state_slots[s] * (taps - 1) * C, r0, n, c);
 }
 
 VOB_EXPORT int vob_conv_state_update(const void* proj, int code, long ld, int x_off, int C, int taps, float* cstate,
@@ -300,7 +318,8 @@ __global__ void __launch_bounds__(128, 1)
 recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restrict__ k, long ld_k, const TV* __restrict__ v,
                        long ld_v, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ u,
                        float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
-                       float* __restrict__ o, int H, int K, int V, int rk_div) {
+                       float* __restrict__ o, int H, int K, int V, int rk_div, const TV* __restrict__ conv_x, long ld_cx, int conv_c,
+                       int conv_taps, float* __restrict__ conv_state) {
     // Every size of the tiling is a constant, so that staging a token is a few plain loads and stores: what one token
     // needs is one list of PER elements (r, k and in mode 0 w, b, u over KPAD channels, then v over VT columns), thread
     // t takes elements t, t + 128, ... of it (NPT per token), and the list of the next CT tokens is fetched into
@@ -321,6 +340,13 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     if (r1 <= r0) return;
     __shared__ __align__(16) float sm[CT * PER];     // token tt: [r | k | (w | b | u) | v | (strength)] at sm + tt * PER
     const int tid = threadIdx.x;
+    if (MODE == 2 && conv_x) {
+        // the convolutions' last inputs of this request (the kernel that read the old ones has completed)
+        float* st = conv_state + (size_t)state_slots[s] * (conv_taps - 1) * conv_c;
+        const int blocks = gridDim.x * gridDim.y;
+        for (int c = (blockIdx.y * gridDim.x + blockIdx.x) * 128 + tid; c < conv_c; c += blocks * 128)
+            conv_state_shift(conv_x, ld_cx, conv_c, conv_taps, st, r0, r1 - r0, c);
+    }
     const int q = tid % KS, jj = tid / KS;
     const int j = blockIdx.x * VT + jj;
     const bool col = j < V;
@@ -467,11 +493,11 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
 template <int MODE, typename TRK, typename TV>
 static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const void* v, long ld_v, const float* w, const float* b,
                        const float* u, float* state, const int* seq_starts, const int* state_slots, float* o, int seqs, int H, int K,
-                       int V, int rk_div, cudaStream_t stream) {
+                       int V, int rk_div, const void* conv_x, long ld_cx, int conv_c, int conv_taps, float* conv_state, cudaStream_t stream) {
 #define VOB_SCAN(P, KS_)                                                                                                        \
     return vob_launch(recurrence_scan_kernel<MODE, P, KS_, TRK, TV>, dim3((V + 128 / KS_ - 1) / (128 / KS_), H, seqs), dim3(128), 0,  \
                       stream, (const TRK*)r, ld_r, (const TRK*)k, ld_k, (const TV*)v, ld_v, w, b, u, state, seq_starts, state_slots, o, \
-                      H, K, V, rk_div)
+                      H, K, V, rk_div, (const TV*)conv_x, ld_cx, conv_c, conv_taps, conv_state)
     if (K <= 32) VOB_SCAN(8, 4);
     if (K <= 64) VOB_SCAN(16, 4);
     if (K <= 128) VOB_SCAN(16, 8);
@@ -482,7 +508,8 @@ static int scan_launch(const void* r, long ld_r, const void* k, long ld_k, const
 
 VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const void* k, long ld_k, int rk_code, const void* v, long ld_v,
                                    int v_code, const float* w, const float* b, const float* u, float* state, const int* seq_starts,
-                                   const int* state_slots, float* o, int seqs, int H, int K, int V, int rk_div, cudaStream_t stream) {
+                                   const int* state_slots, float* o, int seqs, int H, int K, int V, int rk_div, const void* conv_x,
+                                   long ld_cx, int conv_c, int conv_taps, float* conv_state, cudaStream_t stream) {
     if (seqs <= 0) return 0;
     if (H <= 0 || K <= 0 || V <= 0 || H > 65535 || seqs > 65535) return VOB_ERR_BAD_ARG;
     if (K > 512) return VOB_ERR_UNSUPPORTED;
@@ -490,7 +517,10 @@ VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const voi
     if (mode == 1 && !w) return VOB_ERR_BAD_ARG;
     if (mode == 2 && (!w || !b)) return VOB_ERR_BAD_ARG;
     if (rk_div <= 0 || H % rk_div != 0 || (mode != 2 && rk_div != 1)) return VOB_ERR_BAD_ARG;
-#define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, rk_div, stream
+    // conv_x (mode 2, optional): columns of the activations' type (v's) whose last conv_taps - 1 rows per request are
+    // left in conv_state [slots, conv_taps - 1, conv_c]
+    if (conv_x && (mode != 2 || conv_c <= 0 || conv_taps < 2 || !conv_state)) return VOB_ERR_BAD_ARG;
+#define VOB_ARGS r, ld_r, k, ld_k, v, ld_v, w, b, u, state, seq_starts, state_slots, o, seqs, H, K, V, rk_div, conv_x, ld_cx, conv_c, conv_taps, conv_state, stream
     if (mode == 0 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<0, float, float>(VOB_ARGS);
     if (mode == 0 && rk_code == VOB_BF16 && v_code == VOB_BF16) return scan_launch<0, __nv_bfloat16, __nv_bfloat16>(VOB_ARGS);
     if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<1, float, float>(VOB_ARGS);

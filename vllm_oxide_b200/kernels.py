@@ -426,10 +426,13 @@ def gemm_sm100_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None
 
 
 @_timed
-def gemm_pair_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16) for many rows:
-    the two-SM tcgen05 product whose epilogue applies the activation (gate and up never go to memory)."""
+def gemm_pair_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[T, I] = act(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16) for many rows:
+    the two-SM tcgen05 product whose epilogue applies the activation (gate and up never go to memory);
+    act is "silu" or "gelu_tanh"."""
     op = "gemm_pair_swiglu"
+    if activation not in GLU_ACTIVATIONS:
+        raise ShapeError(op, f"activation {activation!r} is not known ({', '.join(GLU_ACTIVATIONS)})")
     _cuda(op, a, w_gate_up, out)
     if not gemm_sm100_supported(a, w_gate_up):
         raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
@@ -439,9 +442,9 @@ def gemm_pair_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
     I = w_gate_up.shape[0] // 2
     if out.shape != (T, I) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise ShapeError(op, f"out must be bfloat16 [{T}, {I}], got {out.dtype} {list(out.shape)}")
-    f = _fn("gemm_sm100_pair", "vob_gemm_sm100_pair_swiglu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P])
+    f = _fn("gemm_sm100_pair", "vob_gemm_sm100_pair_glu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P])
     _check(f(_ptr(a), a.stride(0), _ptr(w_gate_up), w_gate_up.stride(0), _ptr(out), out.stride(0), T, I, K,
-             _ptr(_scratch_for(a.device).err), _stream()), op)
+             GLU_ACTIVATIONS[activation], _ptr(_scratch_for(a.device).err), _stream()), op)
 
 
 def _pick_splits(T: int, N: int, K: int, device) -> int:
@@ -453,10 +456,13 @@ FUSED_GEMM_MAX_ROWS = 64      # what the fused kernels take
 
 
 @_timed
-def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
-    """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16): one tcgen05
-    kernel with two accumulators whose epilogue applies the activation, for at most 64 rows."""
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
+                activation: str = "silu") -> None:
+    """out[T, I] = act(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K], bfloat16): one tcgen05
+    kernel with two accumulators whose epilogue applies the activation ("silu" or "gelu_tanh"), for at most 64 rows."""
     op = "gemm_swiglu"
+    if activation not in GLU_ACTIVATIONS:
+        raise ShapeError(op, f"activation {activation!r} is not known ({', '.join(GLU_ACTIVATIONS)})")
     _cuda(op, a, w_gate_up, out)
     if not gemm_sm100_supported(a, w_gate_up):
         raise ShapeError(op, "operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
@@ -470,9 +476,9 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, spl
         raise ShapeError(op, f"out must be bfloat16 [{T}, {I}], got {out.dtype} {list(out.shape)}")
     if splits is None:
         splits = _pick_splits(T, 2 * I, K, a.device)
-    f = _fn("gemm_sm100", "vob_gemm_sm100_swiglu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P])
+    f = _fn("gemm_sm100", "vob_gemm_sm100_glu", [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _P])
     _check(f(_ptr(a), a.stride(0), _ptr(w_gate_up), w_gate_up.stride(0), _ptr(out), out.stride(0), T, I, K, int(splits),
-             _ptr(_scratch_for(a.device).err), _stream()), op)
+             GLU_ACTIVATIONS[activation], _ptr(_scratch_for(a.device).err), _stream()), op)
 
 
 def gemm_qkv_rope_supported(head_dim: int) -> bool:
@@ -529,7 +535,7 @@ class _EpiArgs(ctypes.Structure):
                 ("ssq_in", _P), ("resid", _P), ("next_w", _P), ("xn_out", _P), ("ssq_out", _P),
                 ("ld_resid", _L), ("ld_xn", _L),
                 ("q_dim", _I), ("kv_dim", _I), ("hd", _I), ("KV", _I), ("page_size", _I),
-                ("ssq_tiles", _I), ("ld_ssq", _I), ("inv_h", _F), ("eps", _F), ("pad_", _I),
+                ("ssq_tiles", _I), ("ld_ssq", _I), ("inv_h", _F), ("eps", _F), ("act", _I),
                 ("temperature", _P), ("seeds", _P), ("steps", _P), ("part_val", _P), ("part_idx", _P), ("nan_flags", _P),
                 ("ld_part", _L)]
 
@@ -822,14 +828,17 @@ def rotate_scale(src: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Ten
 @_timed
 def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
                     u: Optional[torch.Tensor], state: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor,
-                    num_seqs: int, heads: int, out: torch.Tensor, rk_heads: Optional[int] = None) -> None:
+                    num_seqs: int, heads: int, out: torch.Tensor, rk_heads: Optional[int] = None, conv_x: Optional[torch.Tensor] = None,
+                    conv_state: Optional[torch.Tensor] = None) -> None:
     """The recurrence over each request's rows of this step, from and to its state slot.
     mode 0: S = diag(w_t) S - b_t (u_t^T S) + k_t v_t^T with w, b, u float32 [T, heads * K];
     mode 1: S = w[h] S + k_t v_t^T with w float32 [heads];
     mode 2: S' = diag(w_t) S; S = S' + k_t (b_t (v_t - S'^T k_t))^T with w float32 [T, heads * K], b float32
     [T, heads], and r, k float32 [T, rk_heads * K] (head h reads r and k of head h // (heads / rk_heads)).
     o_t = S^T r_t -> out float32 [T, heads * V].
-    state float32 [slots, heads, K, V]; r, k [T, heads * K] and v [T, heads * V] with any row stride."""
+    state float32 [slots, heads, K, V]; r, k [T, heads * K] and v [T, heads * V] with any row stride.
+    Mode 2 with `conv_x` ([T, C] of v's type, any row stride) and `conv_state` (float32 [slots, taps - 1, C]) also does
+    what `conv_state_update` does, on its way."""
     op = "recurrence_scan"
     _cuda(op, r, k, v, w, b, u, state, seq_starts, state_slots, out)
     for name, t in (("r", r), ("k", k), ("v", v)):
@@ -862,9 +871,20 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         raise ShapeError(op, f"mode {mode} is not known")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(state_slots, num_seqs, op, "state_slots")
-    f = _fn("recurrence", "vob_recurrence_scan", [_I, _P, _L, _P, _L, _I, _P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+    conv_c = conv_taps = 0
+    if conv_x is not None:
+        _cuda(op, conv_x, conv_state)
+        _rows_2d(conv_x, op, "conv_x")
+        if (mode != 2 or conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 3 or not conv_state.is_contiguous()
+                or conv_state.shape[1] < 1 or conv_x.shape != (T, conv_state.shape[2]) or conv_x.dtype != v.dtype):
+            raise ShapeError(op, "conv_x [T, C] of v's type goes with mode 2 and a contiguous float32 conv_state [slots, taps - 1, C]")
+        conv_c, conv_taps = conv_state.shape[2], conv_state.shape[1] + 1
+    f = _fn("recurrence", "vob_recurrence_scan", [_I, _P, _L, _P, _L, _I, _P, _L, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                                                  _P, _L, _I, _I, _P, _P])
     _check(f(mode, _ptr(r), r.stride(0), _ptr(k), k.stride(0), _code(r, op), _ptr(v), v.stride(0), _code(v, op), _ptr(w), _ptr(b), _ptr(u),
-             _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), num_seqs, heads, K, V, heads // rk_heads, _stream()), op)
+             _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), num_seqs, heads, K, V, heads // rk_heads,
+             _ptr(conv_x), conv_x.stride(0) if conv_x is not None else 0, conv_c, conv_taps,
+             _ptr(conv_state) if conv_x is not None else _P(0), _stream()), op)
 
 
 @_timed

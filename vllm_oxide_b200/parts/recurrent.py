@@ -220,10 +220,10 @@ class GatedDelta(Mixer):
         decay, strength = ctx.alloc((T, hk), torch.float32), ctx.alloc((T, self.H), torch.float32)
         kernels.gated_delta_prep(proj, 0, self.b_off, low, 0, self.conv_w, conv_state, self.a_log, self.dt_bias, ctx.positions, ctx.row_seq,
                                  ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, self.G, self.K, self.V, q, k, v, decay, strength)
-        if conv_state is not None:
-            kernels.conv_state_update(proj, 0, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
         o = ctx.alloc((T, hv), torch.float32)
-        kernels.recurrence_scan(2, q, k, v, decay, strength, None, S, ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, o, rk_heads=self.G)
+        # the scan also leaves the convolutions' last inputs in the request's slot (the preparation has read the old ones)
+        kernels.recurrence_scan(2, q, k, v, decay, strength, None, S, ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, o, rk_heads=self.G,
+                                conv_x=proj[:, :self.C] if conv_state is not None else None, conv_state=conv_state)
         kernels.recurrence_post(o, low[:, hk:], self.norm_weight, "sigmoid", self.eps, self.H, pre_out, out_scale)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state, out=None) -> torch.Tensor:

@@ -1,8 +1,8 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), dense, no bias; act is silu (SwiGLU,
 crates/engine/src/model.rs:325-331; activation crates/engine/src/backend/cpu/mod.rs:341-349) or,
 with `activation="gelu_tanh"`, the tanh form of gelu. gate and up are one fused matrix
-[Wgate; Wup], so a single product feeds the activation. The products whose epilogue applies the
-activation are built for silu; any other activation runs the product and the activation kernel."""
+[Wgate; Wup], so a single product feeds the activation; the products whose epilogue applies the
+activation take either. (The folded form of a step of few rows is built for silu.)"""
 from __future__ import annotations
 
 import torch
@@ -36,7 +36,7 @@ class SwiGLU(FeedForward):
         """Which kernels a step of `rows` rows runs: "few" (one tcgen05 kernel, activation in its
         epilogue), "pair" (the two-SM product with the activation in its epilogue) or "separate"
         (a product to gate|up, then the activation kernel)."""
-        ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0 and self.activation == "silu"
+        ok = self.dtype == torch.bfloat16 and self.fused and aligned_input and self.hidden % 8 == 0
         if ok and rows <= TUNING.few_rows:
             return "few"
         if ok and rows >= TUNING.pair_gemm_from_rows:
@@ -84,11 +84,11 @@ class SwiGLU(FeedForward):
         path = self._path(T, kernels.gemm_sm100_supported(x, self.w_gate_up))
         if path == "few":
             # few rows: one kernel, the activation applied in the product's epilogue
-            kernels.gemm_swiglu(x, self.w_gate_up, act)
+            kernels.gemm_swiglu(x, self.w_gate_up, act, activation=self.activation)
         elif path == "pair":
             # many rows: the two-SM product with the activation in its epilogue (gate and up never
             # go to memory)
-            kernels.gemm_pair_swiglu(x, self.w_gate_up, act)
+            kernels.gemm_pair_swiglu(x, self.w_gate_up, act, self.activation)
         else:
             gate_up = matmul(x, self.w_gate_up, ctx.alloc((T, 2 * self.inter)))
             kernels.glu(gate_up, act, self.activation)
