@@ -205,7 +205,7 @@ def _fill(cache, tables, s, x, page):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,DV,window,sink,gate", [
-    (4, 2, 24, 40, 0, True, False), (3, 3, 10, 6, 5, False, True), (8, 2, 64, 64, 40, False, True), (4, 1, 96, 48, 0, True, False),
+    (4, 2, 24, 40, 0, True, False), (3, 3, 10, 6, 5, False, True), (8, 4, 64, 64, 45, False, True), (6, 3, 80, 56, 0, True, False),
     (6, 2, 32, 48, 37, True, True), (2, 1, 128, 16, 1, False, False), (8, 2, 64, 64, 0, True, False), (4, 2, 128, 128, 0, True, True),
     (4, 1, 128, 128, 100, False, False)])
 def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, G, D, DV, window, sink, gate):
@@ -311,7 +311,7 @@ def test_attention_preparation_rotation_norm_factor_mixing_and_cache_write(dtype
     H, G, D, DV, page, T = 3, 1, 20, 12, 4, 9
     rot, base, eps = 8, 50.0, 1e-5
     proj = (torch.randn(T, 5 + H * D + G * D + G * DV)).to(dtype)
-    pos = torch.tensor([0, 1, 2, 3, 254, 255, 256, 1023, -1], dtype=torch.int32)
+    pos = torch.tensor([0, 1, 2, 3, 126, 127, 128, 1023, -1], dtype=torch.int32)
     slots = torch.tensor([5, 6, 7, 0, 17, 18, 19, 2, -1], dtype=torch.int32)
     kc = torch.full((6, G, page, D), float("nan"), dtype=dtype, device=DEV)
     vc = torch.full((6, G, page, DV), float("nan"), dtype=dtype, device=DEV)
@@ -319,7 +319,7 @@ def test_attention_preparation_rotation_norm_factor_mixing_and_cache_write(dtype
     inv = torch.from_numpy(rotary_inv_freq(rot, base).copy()).to(DEV)
     first = torch.randn(T, G * DV).to(dtype)
     lam = torch.tensor([0.3], device=DEV)
-    kernels.flex_prep(proj.to(DEV), 5, 5 + H * D, 5 + H * D + G * D, pos.to(DEV), slots.to(DEV), inv, rot, True, eps, (0.5, 256),
+    kernels.flex_prep(proj.to(DEV), 5, 5 + H * D, 5 + H * D + G * D, pos.to(DEV), slots.to(DEV), inv, rot, True, eps, (0.4, 128),
                       lam, first.to(DEV), 2, qo, kc, vc, H, G, D, DV)
     p64 = proj.double()
 
@@ -330,7 +330,7 @@ def test_attention_preparation_rotation_norm_factor_mixing_and_cache_write(dtype
             out[t] = z[max(int(pos[t]), 0)]
         return plain.rms(out, eps)
     q = rotated(p64[:, 5:5 + H * D], H)
-    fac = 1.0 + 0.5 * torch.log((torch.div(pos.clamp(min=0) + 1, 256, rounding_mode="floor") + 1).double())
+    fac = 1.0 + 0.4 * torch.log((torch.div(pos.clamp(min=0) + 1, 128, rounding_mode="floor") + 1).double())
     q = q * fac[:, None, None]
     k = rotated(p64[:, 5 + H * D:5 + H * D + G * D], G)
     v = 0.7 * p64[:, -G * DV:] + 0.3 * first.double()
