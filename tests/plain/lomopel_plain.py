@@ -92,7 +92,7 @@ def sink_attention(h, t, p, m, v_first=None):
 
 
 def window_attention(h, t, p, m, eps):
-    """Attention over the last `mask.size` tokens (itself included): rotary positions on part of each
+    """Attention over the last `mask.size` tokens (itself included; all earlier ones without `mask`): rotary positions on part of each
     head, then q and k divided by their root mean square per head, ordinary softmax, and a sigmoid
     gate from the same input on the heads' results before the output projection."""
     T = h.shape[0]
@@ -106,7 +106,9 @@ def window_attention(h, t, p, m, eps):
     q, k = rms(q, eps), rms(k, eps)
     i = torch.arange(T)
     dist = i[:, None] - i[None, :]
-    visible = (dist >= 0) & (dist < m["mask"]["size"])
+    visible = dist >= 0
+    if m.get("mask"):
+        visible = visible & (dist < m["mask"]["size"])
     o = attend(q, k, v, m["scale"], visible).reshape(T, H * dv)
     return (o * torch.sigmoid(h @ t[p + "g"].T)) @ t[p + "o"].T
 
