@@ -30,7 +30,7 @@ VOB_PDL_SWITCH(attention_flex)
 // ---------------------------------------------------------------------------------------------
 // NI: features a lane holds of a q or k head, 32 * NI >= D.
 template <typename T, int NI>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const int* __restrict__ positions,
                  const int* __restrict__ slots, const float* __restrict__ inv_freq, int rot, int unit_rms, float eps,
                  float temp_coef, int temp_every, const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode,
@@ -64,8 +64,8 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
             for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
                 if (f < rot) {
-                    float sn, cs;
-                    sincosf(fpos * inv_freq[f < half ? f : f - half], &sn, &cs);
+                    const float ang = fpos * inv_freq[f < half ? f : f - half];
+                    const float sn = sinf(ang), cs = cosf(ang);
                     x[i] = f < half ? x[i] * cs - y[i] * sn : x[i] * cs + y[i] * sn;
                 }
                 ss = fmaf(x[i], x[i], ss);

@@ -444,10 +444,13 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                     S[4 * i + 3] = fmaf(kk[4 * i + 3], vj, fmaf(ww.w, S[4 * i + 3], -(bb.w * dot)));
                 }
             } else if (MODE == 2) {
-                // decay first, then the delta-rule write against the decayed state, in this order
+                // Decay first, then the delta-rule write against the decayed state S'. The read-out sees the write:
+                // o = (S' + k uu)^T r = S'^T r + (k . r) uu, so the three sums over key channels (k . S', r . S', k . r)
+                // are taken in one pass and finished by ONE round of shuffles, and the token-to-token chain is
+                // decay -> sums -> shuffles -> write (the read-out hangs off it instead of lengthening it).
                 const float4* pw = reinterpret_cast<const float4*>(sm + tt * PER + 2 * KPADP + q * GRP);
                 const float strength = sm[tt * PER + NA * KPADP + VT];
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f, e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f, f0 = 0.f, f1 = 0.f, f2 = 0.f, f3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < KPT / 4; ++i) {
                     const float4 ww = pw[i];
@@ -456,13 +459,27 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                     d1 = fmaf(kk[4 * i + 1], S[4 * i + 1], d1);
                     d2 = fmaf(kk[4 * i + 2], S[4 * i + 2], d2);
                     d3 = fmaf(kk[4 * i + 3], S[4 * i + 3], d3);
+                    e0 = fmaf(rr[4 * i], S[4 * i], e0);
+                    e1 = fmaf(rr[4 * i + 1], S[4 * i + 1], e1);
+                    e2 = fmaf(rr[4 * i + 2], S[4 * i + 2], e2);
+                    e3 = fmaf(rr[4 * i + 3], S[4 * i + 3], e3);
+                    f0 = fmaf(rr[4 * i], kk[4 * i], f0);
+                    f1 = fmaf(rr[4 * i + 1], kk[4 * i + 1], f1);
+                    f2 = fmaf(rr[4 * i + 2], kk[4 * i + 2], f2);
+                    f3 = fmaf(rr[4 * i + 3], kk[4 * i + 3], f3);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
+                float dot = (d0 + d1) + (d2 + d3), read = (e0 + e1) + (e2 + e3), rk = (f0 + f1) + (f2 + f3);
 #pragma unroll
-                for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                for (int off = 1; off < KS; off <<= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                    read += __shfl_xor_sync(0xffffffffu, read, off);
+                    rk += __shfl_xor_sync(0xffffffffu, rk, off);
+                }
                 const float uu = strength * (vj - dot);
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], uu, S[i]);
+                if (q == 0 && col) o[(size_t)(c0 + tt) * H * V + h * V + j] = fmaf(rk, uu, read);
+                continue;
             } else {
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], vj, decay * S[i]);
