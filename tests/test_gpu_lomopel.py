@@ -280,13 +280,22 @@ def test_attention_kernels_far_key_page_borders_window_edges_and_sink(dtype, H, 
             assert float(w[1].sum(-1).max()) < 1e-3      # the sink took it all
         r0 += lens[s]
     assert bool(torch.isnan(wide[:, :8]).all())
-    if dtype != torch.bfloat16 or D != DV or D not in kernels.TENSOR_CORE_HEAD_DIMS:
+    if dtype != torch.bfloat16:
         return
     # the same rows through the tensor-core kernels, which end with the same sink, gate and factor
     want = torch.cat(wants)
     starts = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
     ctxd = torch.tensor(ctxs, dtype=torch.int32, device=DEV)
     skd = sk.to(DEV) if sink else None
+    assert kernels.attn_prefill_mma_any_supported(H, G, D, DV, page) == (D % 8 == 0 and DV % 8 == 0)
+    if kernels.attn_prefill_mma_any_supported(H, G, D, DV, page):
+        # keys and values of sizes of their own, in tiles padded with zero columns
+        out.fill_(float("nan"))
+        kernels.attn_prefill_mma_any(qd, out, kc, vc, tables.to(DEV), starts, ctxd, 2, lens[0], H, G, D, DV, scale, window, skd, gd, 0.75)
+        assert max_rel_diff(out.cpu(), want) < tol
+        assert bool(torch.isnan(wide[:, :8]).all())
+    if D != DV or D not in kernels.TENSOR_CORE_HEAD_DIMS:
+        return
     out.fill_(float("nan"))
     kernels.attn_prefill_mma(qd, out, kc, vc, tables.to(DEV), starts, ctxd, 2, lens[0], H, G, D, scale, window, skd, gd, 0.75)
     assert max_rel_diff(out.cpu(), want) < tol

@@ -338,6 +338,152 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same for keys of D and values of DV features (multiples of 8 up to 128, different or not): the tiles in
+// shared memory are HD = D rounded up to a multiple of 32 and HDV = DV rounded up to 32, 64 or 128 wide, the
+// columns beyond the real sizes zero (a zero column of Q and K adds nothing to a score, a zero column of V
+// gives an output column that is not stored). Same grid, same walk over the key tiles, same tail.
+// ---------------------------------------------------------------------------------------------
+template <int W>
+__device__ __forceinline__ void load_rows_padded(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ cache, int real, const int* s_pages,
+                                                 int page0, int kvh, int KV, int page_shift, int tile_start, int lo, int hi) {
+    constexpr int LD = W + 8, CH = W / 8;
+    const int page_size = 1 << page_shift, real_ch = real >> 3;
+    for (int idx = threadIdx.x; idx < BN * CH; idx += NTHREADS) {
+        const int key = idx / CH, ch = idx - key * CH;
+        const int j = tile_start + key;
+        __nv_bfloat16* d = dst + key * LD + ch * 8;
+        if (ch < real_ch && j >= lo && j < hi) {
+            const int page = s_pages[(j >> page_shift) - page0];
+            cp_async16(d, cache + ((((size_t)page * KV + kvh) << page_shift) + (j & (page_size - 1))) * real + ch * 8);
+        } else {
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+template <int HD, int HDV>
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
+                            long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                            const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
+                            const int* __restrict__ context_lens, int H, int KV, int D, int DV, int page_shift, int window,
+                            float scale_log2, AttnTail tail) {
+    constexpr int LD = HD + 8, LDV = HDV + 8;
+    constexpr int BM = 64;
+    pdl_launch_dependents();
+    pdl_wait(9);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sK0 = sQ + BM * LD;
+    __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
+    int* s_pages = reinterpret_cast<int*>(sV0 + 2 * BN * LDV);            // [max_pages]
+
+    const int G = H / KV;
+    const int kvh = blockIdx.x, seq = blockIdx.y;
+    const int row0 = seq_starts[seq];
+    const int n_new = seq_starts[seq + 1] - row0;
+    const int total_rows = n_new * G;
+    const int tile_row0 = (gridDim.z - 1 - blockIdx.z) * BM;
+    if (tile_row0 >= total_rows) return;
+    const int ctx = context_lens[seq];
+    const int* bt = block_tables + (size_t)seq * max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int c = threadIdx.x; c < BM * (HD / 8); c += NTHREADS) {
+        int r = c / (HD / 8), ch = c - r * (HD / 8);
+        int rr = tile_row0 + r;
+        __nv_bfloat16* dst = sQ + r * LD + ch * 8;
+        if (rr < total_rows && ch * 8 < D) {
+            int tok = rr / G, head = kvh * G + rr % G;
+            cp_async16(dst, q + (size_t)(row0 + tok) * q_stride + (size_t)head * D + ch * 8);
+        } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    const int last_rr = min(tile_row0 + BM, total_rows) - 1;
+    const int hi = ctx + last_rr / G + 1;
+    const int first_tok_pos = ctx + tile_row0 / G;
+    const int lo_blk = window > 0 ? max(0, first_tok_pos + 1 - window) : 0;
+    const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
+    const int page0 = lo_blk >> page_shift, page_end = ((hi - 1) >> page_shift) + 1;
+    for (int i = threadIdx.x; i < page_end - page0; i += NTHREADS) s_pages[i] = bt[page0 + i];
+    __syncthreads();
+
+    load_rows_padded<HD>(sK0, kc, D, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
+    load_rows_padded<HDV>(sV0, vc, DV, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
+    cp_async_commit();
+
+    int pos[2], lo[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
+        pos[h] = rr < total_rows ? ctx + rr / G : -1;
+        lo[h] = window > 0 ? max(0, pos[h] + 1 - window) : 0;
+    }
+    int warp_last_pos = max(pos[0], pos[1]), warp_first_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
+#pragma unroll
+    for (int x = 4; x < 32; x <<= 1) {
+        warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
+        warp_first_pos = min(warp_first_pos, __shfl_xor_sync(0xffffffffu, warp_first_pos, x));
+        warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, x));
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HDV / 8][4];
+#pragma unroll
+    for (int n = 0; n < HDV / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+    uint32_t qf[HD / 16][4];
+
+    for (int t = t_begin; t < t_end; ++t) {
+        int buf = (t - t_begin) & 1;
+        __nv_bfloat16* sK = sK0 + buf * BN * LD;
+        __nv_bfloat16* sV = sV0 + buf * BN * LDV;
+        cp_async_wait<0>();
+        __syncthreads();                       // tile t (and Q) visible; everyone is done with tile t-1
+        if (t + 1 < t_end) {
+            load_rows_padded<HD>(sK0 + (buf ^ 1) * BN * LD, kc, D, s_pages, page0, kvh, KV, page_shift, (t + 1) * BN, lo_blk, hi);
+            load_rows_padded<HDV>(sV0 + (buf ^ 1) * BN * LDV, vc, DV, s_pages, page0, kvh, KV, page_shift, (t + 1) * BN, lo_blk, hi);
+            cp_async_commit();
+        }
+        if (t == t_begin) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+                ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
+        }
+        if (t * BN <= warp_last_pos) {
+            float s[8][4];
+            qk_tile<HD, 8>(s, qf, sK, 0);
+            uint32_t pa[4][4];
+            if ((t + 1) * BN - 1 <= warp_first_pos && t * BN >= warp_max_lo)
+                softmax_step<8, HDV / 8, false>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+            else
+                softmax_step<8, HDV / 8, true>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+            pv_tile<HDV, 4>(o, pa, sV, 0);
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
+        if (rr >= total_rows) continue;
+        int tok = rr / G, head = kvh * G + rr % G;
+        float inv = 1.0f / tail_den(tail, head, l[h], m[h]);
+        __nv_bfloat16* op = out + (size_t)(row0 + tok) * out_stride + (size_t)head * DV + (lane & 3) * 2;
+        const int col = head * DV + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < HDV / 8; ++n)
+            if (n * 8 + (lane & 3) * 2 < DV)
+                *reinterpret_cast<uint32_t*>(op + n * 8) = pack_bf16(tail_val(tail, row0 + tok, col + n * 8, o[n][2 * h] * inv),
+                                                                     tail_val(tail, row0 + tok, col + n * 8 + 1, o[n][2 * h + 1] * inv));
+    }
+}
+
 constexpr int DEC_MIN_TILES = 3;            // measured on whole decode steps at batch 1: 8,192 keys 0.808 ms with 3, 0.838 with 2, 0.812 with 4
 constexpr int DEC_MAX_SPLITS_WIDE = 64;
 
@@ -746,6 +892,23 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
                                    window, scale, splits, partials, arrived, tail, stream);
 }
 
+template <int HD, int HDV>
+int launch_prefill_any(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
+                       const int* bt, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new,
+                       int H, int KV, int D, int DV, int page_size, int window, float scale, AttnTail tail, cudaStream_t stream) {
+    static size_t configured = 0;
+    size_t smem = ((size_t)(64 + 2 * BN) * (HD + 8) + (size_t)2 * BN * (HDV + 8)) * sizeof(__nv_bfloat16) + (size_t)max_pages * sizeof(int);
+    int e = ensure_smem(attn_prefill_mma_any_kernel<HD, HDV>, smem, &configured);
+    if (e) return e;
+    const long long row_tiles = ((long long)max_new * (H / KV) + 63) / 64;
+    if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
+    dim3 grid(KV, S, (unsigned)row_tiles);
+    return vob_launch(attn_prefill_mma_any_kernel<HD, HDV>, grid, dim3(NTHREADS), smem, stream,
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, D, DV, log2_exact(page_size), window,
+        scale * 1.4426950408889634f, tail);
+}
+
 bool sizes_ok(int H, int KV, int hd, int page_size) {
     return (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && page_size > 0 && BN % page_size == 0;
 }
@@ -772,6 +935,35 @@ VOB_EXPORT int vob_attn_prefill_mma(const void* q, long long q_stride, void* out
                                            context_lens, S, max_new, H, KV, page_size, window, scale, tail, stream);
     return launch_prefill<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,
                                context_lens, S, max_new, H, KV, page_size, window, scale, tail, stream);
+}
+
+// Portions of prompts and mixed batches with keys of D and values of DV features, multiples of 8 up to 128 each
+// (kcache [pages, KV, page_size, D], vcache [pages, KV, page_size, DV]); everything else as vob_attn_prefill_mma.
+VOB_EXPORT int vob_attn_prefill_mma_any(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
+                                        const void* vcache, const int* block_tables, int max_pages, const int* seq_starts,
+                                        const int* context_lens, int S, int max_new, int H, int KV, int D, int DV, int page_size,
+                                        int window, float scale, const float* sink, const void* gate, long long gate_stride,
+                                        float out_scale, cudaStream_t stream) {
+    if (S <= 0 || max_new <= 0) return 0;
+    if (KV <= 0 || H % KV != 0 || page_size <= 0 || BN % page_size != 0) return VOB_ERR_UNSUPPORTED;
+    if (D <= 0 || DV <= 0 || D % 8 != 0 || DV % 8 != 0 || D > 128 || DV > 128) return VOB_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || out_stride % 2 != 0 || S > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
+    const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
+#define VOB_ANY(HD_, HDV_)                                                                                                          \
+    return launch_prefill_any<HD_, HDV_>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,          \
+                                         context_lens, S, max_new, H, KV, D, DV, page_size, window, scale, tail, stream)
+#define VOB_ANY_V(HD_)                                                                                                              \
+    do {                                                                                                                            \
+        if (DV <= 32) VOB_ANY(HD_, 32);                                                                                             \
+        if (DV <= 64) VOB_ANY(HD_, 64);                                                                                             \
+        VOB_ANY(HD_, 128);                                                                                                          \
+    } while (0)
+    if (D <= 32) VOB_ANY_V(32);
+    if (D <= 64) VOB_ANY_V(64);
+    if (D <= 96) VOB_ANY_V(96);
+    VOB_ANY_V(128);
+#undef VOB_ANY_V
+#undef VOB_ANY
 }
 
 // `splits` (1..8) blocks share each (request, kv head) as one cluster. With `partials` (float32

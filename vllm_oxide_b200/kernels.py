@@ -1274,6 +1274,55 @@ def attn_prefill_mma(q, out, kcache, vcache, block_tables, seq_starts, context_l
              head_dim, kcache.shape[2], int(window), float(scale), *tail, _stream()), op)
 
 
+def attn_prefill_mma_any_supported(num_heads: int, num_kv_heads: int, dim: int, vdim: int, page_size: int) -> bool:
+    """Whether the portion kernel for keys and values of sizes of their own takes these (bfloat16 only): multiples of 8 up to
+    128 each, a page size that divides 64."""
+    return (num_kv_heads > 0 and num_heads % num_kv_heads == 0 and 0 < dim <= 128 and 0 < vdim <= 128 and dim % 8 == 0
+            and vdim % 8 == 0 and page_size > 0 and 64 % page_size == 0)
+
+
+@_timed
+def attn_prefill_mma_any(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
+                         num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None,
+                         out_scale: float = 1.0) -> None:
+    """Tensor-core attention for portions of prompts and mixed batches (bfloat16) with keys of `dim` and values of `vdim`
+    features: q [T, H * dim], out [T, H * vdim] (any row stride), kcache [pages, KV, page, dim], vcache [pages, KV, page, vdim].
+    The tiles in shared memory are padded with zero columns to the sizes the kernel is built for. Everything else as
+    `attn_prefill_mma`."""
+    op = "attn_prefill_mma_any"
+    if not scale > 0:
+        raise ShapeError(op, f"the score scale must be positive, got {scale}")
+    _cuda(op, q, out, kcache, vcache, block_tables, seq_starts, context_lens)
+    _rows_2d(q, op, "q")
+    _rows_2d(out, op, "out")
+    T = q.shape[0]
+    if any(t.dtype != torch.bfloat16 for t in (q, out, kcache, vcache)):
+        raise ShapeError(op, "the tensor-core attention kernels are bfloat16 only")
+    if q.shape[1] != num_heads * dim or out.shape != (T, num_heads * vdim):
+        raise ShapeError(op, f"q [{T}, {num_heads * dim}] and out [{T}, {num_heads * vdim}] are needed, got {list(q.shape)} and {list(out.shape)}")
+    _kv_caches(op, kcache, vcache, num_kv_heads, dim, vdim, torch.bfloat16)
+    if not attn_prefill_mma_any_supported(num_heads, num_kv_heads, dim, vdim, kcache.shape[2]):
+        raise ShapeError(op, f"sizes not supported: heads {num_heads}/{num_kv_heads}, sizes {dim}/{vdim}, page {kcache.shape[2]}")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous() or block_tables.shape[0] < num_seqs:
+        raise ShapeError(op, f"block_tables must be contiguous int32 [>= {num_seqs}, max_pages]")
+    if q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0 or out.stride(0) % 2 != 0 or out.data_ptr() % 4 != 0:
+        raise ShapeError(op, "q rows must be 16-byte aligned and out rows 4-byte aligned")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(context_lens, num_seqs, op, "context_lens")
+    _cuda(op, q, sink, gate)
+    _f32_vec(sink, num_heads, op, "sink")
+    if gate is not None:
+        _rows_2d(gate, op, "gate")
+        if gate.shape != out.shape or gate.dtype != torch.bfloat16:
+            raise ShapeError(op, f"gate must be bfloat16 {list(out.shape)}, got {gate.dtype} {list(gate.shape)}")
+    f = _fn("attention_mma", "vob_attn_prefill_mma_any",
+            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _L, _F, _P])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+             block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
+             dim, vdim, kcache.shape[2], int(window), float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             float(out_scale), _stream()), op)
+
+
 def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:
     """Whether the tcgen05 attention kernel for prompt portions takes these sizes (bfloat16, no window)."""
     if head_dim not in TENSOR_CORE_HEAD_DIMS:

@@ -129,6 +129,8 @@ class SoftmaxAttention(Mixer):
         mods = ["gemm_sm100", "attention_flex"]
         if self.tensor_core_sizes():
             mods += ["attention_mma"] + ([] if self.window or self.gated else ["attention_sm100"])
+        elif self.D % 8 == 0 and self.DV % 8 == 0 and self.D <= 128 and self.DV <= 128:
+            mods += ["attention_mma"]
         return tuple(mods)
 
     # ------------------------------------------------------------------ the step
@@ -153,8 +155,10 @@ class SoftmaxAttention(Mixer):
         """bfloat16 with keys and values of one size the framework's tensor-core kernels take (64 or 128): steps of
         single tokens go to the split-key decode kernel, portions to the tcgen05 kernel (no window, no gate) or the
         mma.sync one, each of which ends with this mixer's sink, gate and factor; a mixed step's leading single tokens
-        go to the decode kernel and the portions behind them to the portion kernel. Everything else (float32, other
-        sizes) goes to the general kernel."""
+        go to the decode kernel and the portions behind them to the portion kernel. bfloat16 with keys and values of
+        other sizes (multiples of 8 up to 128 each, different or not): portions and mixed steps go to the mma.sync
+        portion kernel that pads its tiles, steps of single tokens to the general kernel. Everything else (float32,
+        other sizes) goes to the general kernel."""
         kc, vc = cache.tensors[0], cache.tensors[1]
         page, bt = kc.shape[2], ctx.block_tables[cache.group]
         H, G, D = self.H, self.G, self.D
@@ -175,6 +179,11 @@ class SoftmaxAttention(Mixer):
                     kernels.attn_prefill_mma(q, out, kc, vc, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:], ctx.seqs - lead,
                                              ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
                 return
+        if (self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0 and not ctx.decode_only and ctx.max_new > 1
+                and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+            kernels.attn_prefill_mma_any(q, out, kc, vc, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs, ctx.max_new, H, G, D, self.DV,
+                                         self.scale, self.window, self.sink, gate, out_scale)
+            return
         kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
                                gate, out_scale)
 
